@@ -5,23 +5,32 @@
 Prints ONE JSON line (rank 0).  Metric: ragged_dot TFLOP/s, 2 * sum(group_sizes) * K * N
 per product (the reference's convention, tokamax/_src/ops/ragged_dot/bench.py:52-56).
 
-Workloads (synthetic, seeded; shapes of tokamax_b200/ragged_dot/arg_specs.py):
-  N = 1 : "cfg2"  Mixtral-8x7B-shaped forward, lhs [16384, 4096] x rhs [8, 4096, 14336], bf16.
-          A step is one forward grouped GEMM.  Inputs (1.07 GB) exceed the 126 MB L2, so
-          every step streams its operands from HBM; no extra L2 flush is done.
-  N > 1 : "ep"    expert-parallel MoE layer, 256 experts sharded over the ranks, per rank
-          8192 tokens x 7168, top-8 routing, local rhs [256/N, 7168, 2048]: all-to-all
-          dispatch (NCCL) -> grouped GEMM -> all-to-all combine.  Weak scaling.
-  --workload cfg2|cfg4|ep overrides the default for the given N.
+Default workload at every N: "ep", the expert-parallel MoE layer -- 256 experts sharded over
+the N ranks, per rank 8192 tokens x 7168 (bf16), top-8 routing, local rhs [256/N, 7168, 2048]:
+route (counting sort) -> dispatch of the token rows to the experts' owners -> grouped GEMM ->
+return of the output rows -> gate-weighted combine.  A step is one call of the layer; per-GPU
+work is fixed as N grows (weak scaling), so the values of N = 1, 2, 4, 8 are the same code
+path on the same per-rank inputs.  Inputs (tokens 117 MB + weights 7.5 GB / N per rank)
+exceed the 126 MB L2, so every step streams its operands from HBM; no extra L2 flush is done.
 
-`value` is timed with inputs resident in HBM (CUDA events on the launching stream, max
-over ranks).  `e2e` is the same work through the public API with pinned HOST buffers:
-every step copies its inputs host->device and the result device->host inside the timed
-region.  `cpu_baseline` (rank 0, N = 1) times the CPU restatement of the reference's
-XLA path on a bounded sample of the same workload with all host threads.
+After the timed region every rank checks the layer's output on sampled tokens against a
+dense top-k MoE recomputed on the host by the CPU oracle, and the group sizes the layer
+derived against the global histogram of all ranks' routing: `parity` in the line; a
+mismatch exits non-zero.
 
---impl reference times that CPU restatement alone (the reference is pure Python over
-jax/jaxlib, which is not installable here: no oracle/_ref exists) on the same workload.
+At N = 1 the line also carries `kernels`: the grouped-GEMM kernels alone on the other named
+workloads (cfg2 Mixtral-shaped forward, cfg3 DeepSeek-V3-shaped fp8 / int8 forward, cfg4
+Qwen3-shaped forward / dlhs / drhs, dsv3 forward / dlhs / drhs and their aggregate), each
+with its time, TFLOP/s, GB/s and the fraction of max(t_flops, t_bytes) at the measured peaks.
+
+`value` is timed with inputs resident in HBM (CUDA events on the launching stream, max over
+ranks).  `e2e` is the same step through the public API with pinned HOST buffers: tokens,
+routing and gates are copied host->device and the result device->host inside the timed
+region.  `cpu_baseline` (rank 0, N = 1) times the CPU restatement of the reference path on
+the host cores.  --impl reference times that CPU restatement alone (the reference is pure
+Python over jax/jaxlib, which is not installable here: no oracle/_ref exists).
+
+--workload cfg1|cfg2|cfg3|cfg4|dsv3 --op fwd|dlhs|drhs times one kernel alone (profiler runs).
 """
 
 from __future__ import annotations
@@ -44,9 +53,9 @@ sys.path.insert(0, ROOT)
 METRIC = "ragged_dot TFLOP/s (2*M*K*N)"
 UNIT = "TFLOP/s"
 
-# DRAM traffic per launch of the forward kernel on cfg2 (dram__bytes_read.sum +
-# dram__bytes_write.sum from an ncu capture; profiles/ragged_gemm_fwd_cfg2_pair.md).
-NCU_TRAFFIC_BYTES = {"cfg2": 2.643e9}
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures,
+# by kernel-suite entry name; None where no capture exists.
+NCU_TRAFFIC_BYTES = {"cfg2.fwd": 2.643e9}
 
 
 # ----------------------------------------------------------------------------- utilities
@@ -68,8 +77,8 @@ class ClockSampler:
             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
             "clocks_event_reasons.sw_power_cap")
 
-  def __init__(self, gpu_index: int):
-    self.gpu_index = gpu_index
+  def __init__(self, gpu_id: str):
+    self.gpu_id = gpu_id
     self.proc = None
     self.lines: list[str] = []
 
@@ -77,7 +86,7 @@ class ClockSampler:
     try:
       self.proc = subprocess.Popen(
           ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
-           "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+           "-i", self.gpu_id], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
       self.thread = threading.Thread(target=self._read, daemon=True)
       self.thread.start()
     except Exception:
@@ -119,14 +128,24 @@ class ClockSampler:
             "samples": len(sm)}
 
 
-def physical_gpu_index(local_index: int) -> int:
+def gpu_id_for_smi(local_index: int) -> str:
+  """What `nvidia-smi -i` should be given for torch's device `local_index`: its UUID (stable
+  under CUDA_VISIBLE_DEVICES in any form), else the physical index."""
+  try:
+    uuid = str(torch.cuda.get_device_properties(local_index).uuid)
+    if uuid and not uuid.startswith("GPU-"):
+      uuid = "GPU-" + uuid
+    if uuid:
+      return uuid
+  except Exception:
+    pass
   vis = os.environ.get("CUDA_VISIBLE_DEVICES")
   if vis:
     try:
-      return int(vis.split(",")[local_index])
+      return str(int(vis.split(",")[local_index]))
     except Exception:
       pass
-  return local_index
+  return str(local_index)
 
 
 def make_cfg_inputs(w, device, seed=0):
@@ -140,94 +159,56 @@ def make_cfg_inputs(w, device, seed=0):
   return lhs, rhs, gs
 
 
-# ----------------------------------------------------------------------------- CPU baseline
-def cpu_grouped_gemm_sample(w, target_seconds: float, threads: int):
-  """Times the CPU restatement of the reference path (oracle.ragged_dot_ref: per-group
-  float32 matmul of bf16-rounded inputs) on the first `frac` of every group's rows.
-  Returns (tflops, description, seconds)."""
-  from oracle import ragged_dot_ref as ref  # the checker, used here as the timed CPU baseline
-  torch.set_num_threads(threads)
-  rng = np.random.default_rng(0)
-  gs = np.asarray(w.group_sizes)
-
-  def build(frac):
-    rows = np.maximum((gs * frac).astype(np.int64), (gs > 0).astype(np.int64))
-    m = int(rows.sum())
-    lhs = torch.from_numpy(rng.standard_normal((m, w.k), dtype=np.float32)).bfloat16()
-    return lhs, rows
-
-  # One expert's weights are reused for every group: the arithmetic and the memory
-  # traffic per group are the same, and the host does not need G x K x N floats.
-  rhs_one = torch.from_numpy((rng.standard_normal((1, w.k, w.n), dtype=np.float32) * w.k ** -0.5)).bfloat16()
-
-  def run(lhs, rows):
-    t0 = time.perf_counter()
-    off = 0
-    for r in rows:
-      if r:
-        ref.ragged_dot_ref(lhs[off:off + r], rhs_one, np.array([r]))
-        off += r
-    return time.perf_counter() - t0
-
-  frac = 1.0 / 64
-  lhs, rows = build(frac)
-  run(lhs, rows)  # warm-up
-  t = run(lhs, rows)
-  flops = 2.0 * rows.sum() * w.k * w.n
-  rate = flops / t
-  full = w.flops / rate
-  frac = float(min(1.0, max(frac, target_seconds / full)))
-  lhs, rows = build(frac)
-  t = run(lhs, rows)
-  flops = 2.0 * rows.sum() * w.k * w.n
-  desc = (f"{w.name}: first {frac:.4f} of every group's rows ({int(rows.sum())} of {w.m} rows), "
-          f"per-group float32 matmul of bf16 inputs, {threads} threads")
-  return flops / t / 1e12, desc, t
+def time_region(step, stream, launches: int, sampler_id: str | None, min_region_ms: float = 0.0):
+  """Runs `step` `launches` times between two CUDA events on `stream`; returns (ms per launch,
+  launches timed, clock summary).  With `min_region_ms` the count is raised so that the region
+  lasts at least that long (the 100 ms clock sampler has to see it)."""
+  for _ in range(3):
+    step()
+  torch.cuda.synchronize()
+  if min_region_ms > 0:
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record(stream)
+    for _ in range(3):
+      step()
+    e.record(stream)
+    torch.cuda.synchronize()
+    est = max(s.elapsed_time(e) / 3, 1e-3)
+    launches = max(launches, int(np.ceil(min_region_ms / est)))
+  ctx = ClockSampler(sampler_id) if sampler_id is not None else None
+  if ctx is not None:
+    ctx.__enter__()
+  try:
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    s.record(stream)
+    for _ in range(launches):
+      step()
+    e.record(stream)
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / launches
+  finally:
+    if ctx is not None:
+      ctx.__exit__(None, None, None)
+  return ms, launches, (ctx.summary() if ctx is not None else None)
 
 
-def run_reference_arm(args, w, world, rank):
-  if rank != 0:
-    return None
-  threads = os.cpu_count() or 1
-  per_step = 2.0
-  vals = []
-  desc = ""
-  for i in range(args.warmup + args.steps):
-    tf, desc, t = cpu_grouped_gemm_sample(w, per_step, threads)
-    if i >= args.warmup:
-      vals.append((tf, t))
-  tf = float(np.median([v[0] for v in vals]))
-  ms = float(np.mean([v[1] for v in vals]) * 1e3)
-  line = {
-      "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus,
-      "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-      "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-      "config": {"workload": w.name, "note": w.note, "m": w.m, "k": w.k, "n": w.n, "g": w.g,
-                 "reference_path": "CPU restatement of implementation='xla' (jax not installable here)"},
-      "cpu_baseline": {"value": tf, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
-      "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-      "gpu_launches": 0,
-  }
-  return line
-
-
-# ----------------------------------------------------------------------------- single GPU
-def run_single(args, w, peaks):
+# ----------------------------------------------------------------------------- one kernel alone
+def build_kernel_step(w, op_name: str, dev, fp8_path: str = "native"):
+  """Inputs and a launch closure for one contraction of workload `w` through the C ABI.
+  Returns (step, algorithmic bytes per launch, config repr, tensors to keep alive)."""
   from tokamax_b200 import _capi
-  import tokamax_b200 as tk
+  from tokamax_b200.quantization import QArray, quantize_per_channel
   from tokamax_b200.ragged_dot import b200 as b200_lib
+  from tokamax_b200.ragged_dot import base as base_lib
 
-  dev = torch.device("cuda", 0)
-  torch.cuda.set_device(dev)
-  _capi.load()
   lhs, rhs, gs = make_cfg_inputs(w, dev)
   op = b200_lib.B200RaggedDot()
   quant = w.rhs_dtype in (torch.float8_e4m3fn, torch.int8)
   scale = None
   if quant:
-    if args.op != "fwd":
+    if op_name != "fwd":
       raise SystemExit("8-bit weights are a forward-only workload")
-    from tokamax_b200.quantization import quantize_per_channel
     q = torch.empty(w.g, w.k, w.n, device=dev, dtype=w.rhs_dtype)
     scale = torch.empty(w.g, w.n, device=dev, dtype=torch.float32)
     for g in range(w.g):  # per expert, to bound temporaries
@@ -235,19 +216,20 @@ def run_single(args, w, peaks):
       q[g] = qa.qvalue[0]
       scale[g] = qa.channel_scale()[0]
     rhs = q
-  from tokamax_b200.ragged_dot import base as base_lib
-  from tokamax_b200.quantization import QArray
-  if args.op == "fwd":
+  if op_name == "fwd":
     out = torch.empty(w.m, w.n, device=dev, dtype=torch.bfloat16)
     bound = op.bind(lhs, QArray(rhs, scale) if quant else rhs, group_sizes=gs)
     ccfg = bound.default_config.to_capi()
     workspace = None
-    if quant and args.fp8_path == "native":
+    if quant and fp8_path == "native":
       need = _capi.workspace_bytes(0, w.m, w.k, w.n, w.g, rhs.dtype)
       workspace = torch.empty(need, dtype=torch.uint8, device=dev) if need else None
     step = lambda: _capi.ragged_dot_fwd(lhs, rhs, gs, out, rhs_scale=scale, config=ccfg, workspace=workspace)
-    alg_bytes = w.m * w.k * 2 + w.g * w.k * w.n * rhs.element_size() + w.m * w.n * 2 + (w.g * w.n * 4 if quant else 0)
-  elif args.op == "dlhs":
+    nz = sum(1 for v in w.group_sizes if v > 0)
+    alg_bytes = (w.m * w.k * 2 + nz * w.k * w.n * rhs.element_size() + w.m * w.n * 2
+                 + (nz * w.n * 4 if quant else 0))
+    keep = (lhs, rhs, gs, out, scale, workspace)
+  elif op_name == "dlhs":
     gen = torch.Generator(device=dev).manual_seed(7)
     dout = torch.randn(w.m, w.n, device=dev, generator=gen, dtype=torch.float32).to(torch.bfloat16)
     out = torch.empty(w.m, w.k, device=dev, dtype=torch.bfloat16)
@@ -255,125 +237,250 @@ def run_single(args, w, peaks):
     ccfg = bound.default_config.to_capi()
     step = lambda: _capi.ragged_dot_dlhs(dout, rhs, gs, out, config=ccfg)
     alg_bytes = 2 * (w.m * w.n + w.g * w.k * w.n + w.m * w.k)
+    keep = (dout, rhs, gs, out)
+    del lhs
   else:
     gen = torch.Generator(device=dev).manual_seed(7)
     dout = torch.randn(w.m, w.n, device=dev, generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    del rhs
     out = torch.empty(w.g, w.k, w.n, device=dev, dtype=torch.bfloat16)
     bound = op.bind(lhs, dout, group_sizes=gs,
                     ragged_dot_dimension_numbers=base_lib.RAGGED_CONTRACTING_DOT_DIM_NUMS)
     ccfg = bound.default_config.to_capi()
     step = lambda: _capi.ragged_dot_drhs(lhs, dout, gs, out, config=ccfg)
     alg_bytes = 2 * (w.m * w.k + w.m * w.n + w.g * w.k * w.n)
-  cfg = bound.default_config
-  stream = torch.cuda.current_stream()
-  # Roofline side: the larger of the two times at the measured peaks decides the bound.
-  t_tensor = w.flops / (peaks["bf16"] * 1e12)
-  t_hbm = alg_bytes / (peaks["hbm"] * 1e9)
-  bound_kind = "tensor" if t_tensor >= t_hbm else "hbm"
+    keep = (lhs, dout, gs, out)
+  return step, float(alg_bytes), repr(bound.default_config), keep
 
+
+def roofline_entry(flops: float, alg_bytes: float, ms: float, peaks, peak_tflops: float):
+  """t_roof = max(t_flops, t_bytes) at the measured peaks; frac = t_roof / t_measured."""
+  t_flops = flops / (peak_tflops * 1e12)
+  t_bytes = alg_bytes / (peaks["hbm"] * 1e9)
+  t_roof = max(t_flops, t_bytes)
+  t = ms * 1e-3
+  return {"bound": "tensor" if t_flops >= t_bytes else "hbm", "tflops": flops / t / 1e12,
+          "gbs": alg_bytes / t / 1e9, "frac_tensor": t_flops / t, "frac_hbm": t_bytes / t,
+          "t_roof_ms": t_roof * 1e3, "frac": t_roof / t}
+
+
+def run_kernel_entry(name: str, workload_name: str, op_name: str, dev, peaks, sampler_id, rhs_dtype=None):
+  from tokamax_b200 import _capi
+  from tokamax_b200.ragged_dot import arg_specs
+  w = arg_specs.workload(workload_name)
+  if rhs_dtype is not None:
+    w = dataclasses.replace(w, rhs_dtype=rhs_dtype)
+  entry = {"name": name, "workload": workload_name, "op": op_name, "m": w.m, "k": w.k, "n": w.n, "g": w.g,
+           "rhs_dtype": str(w.rhs_dtype).replace("torch.", "")}
+  try:
+    step, alg_bytes, cfg_repr, keep = build_kernel_step(w, op_name, dev)
+    # >= 50 launches and >= 0.45 s back to back: the 100 ms clock sampler sees the region, and
+    # the part runs at its sustained (power-capped) clocks, so the sustained cuBLAS figure is
+    # the tensor peak to divide by; the fraction of the burst figure is given beside it.
+    ms, launches, clocks = time_region(step, torch.cuda.current_stream(), 50, sampler_id, min_region_ms=450.0)
+    _capi.device_status()
+    rl = roofline_entry(w.flops, alg_bytes, ms, peaks, peaks["bf16_sustained"])
+    rl["tensor_peak"] = "bf16 sustained"
+    rl["frac_vs_burst_peak"] = roofline_entry(w.flops, alg_bytes, ms, peaks, peaks["bf16"])["frac"]
+    entry.update({"ms": ms, "launches": launches, "flops": w.flops, "algorithmic_bytes": alg_bytes,
+                  "tflops": rl["tflops"], "gbs": rl["gbs"], "roofline": rl, "clocks": clocks,
+                  "traffic": NCU_TRAFFIC_BYTES.get(name), "kernel_config": cfg_repr})
+    del step, keep
+  except Exception as e:  # keep the line: one failed entry must not hide the others
+    entry["error"] = f"{type(e).__name__}: {e}"
+  torch.cuda.empty_cache()
+  return entry
+
+
+def run_kernel_suite(dev, peaks, sampler_id):
+  """The grouped-GEMM kernels alone on the named workloads (N = 1 only)."""
+  entries = []
+  plan = [("cfg2.fwd", "cfg2", "fwd", None),
+          ("cfg3.fwd.fp8", "cfg3", "fwd", torch.float8_e4m3fn),
+          ("cfg3.fwd.int8", "cfg3", "fwd", torch.int8),
+          ("cfg4.fwd", "cfg4", "fwd", None), ("cfg4.dlhs", "cfg4", "dlhs", None), ("cfg4.drhs", "cfg4", "drhs", None),
+          ("dsv3.fwd", "dsv3", "fwd", None), ("dsv3.dlhs", "dsv3", "dlhs", None), ("dsv3.drhs", "dsv3", "drhs", None)]
+  for name, wl, op_name, dt in plan:
+    entries.append(run_kernel_entry(name, wl, op_name, dev, peaks, sampler_id, dt))
+  by = {e["name"]: e for e in entries}
+  for wl in ("cfg4", "dsv3"):
+    parts = [by.get(f"{wl}.{o}") for o in ("fwd", "dlhs", "drhs")]
+    if all(p is not None and "ms" in p for p in parts):
+      ms = sum(p["ms"] for p in parts)
+      flops = sum(p["flops"] for p in parts)
+      byts = sum(p["algorithmic_bytes"] for p in parts)
+      rl = roofline_entry(flops, byts, ms, peaks, peaks["bf16_sustained"])
+      # the sum of the three roofs, not the roof of the sums: each kernel has its own bound
+      t_roof = sum(p["roofline"]["t_roof_ms"] for p in parts)
+      rl.update({"t_roof_ms": t_roof, "frac": t_roof / ms})
+      entries.append({"name": f"{wl}.fwd+bwd", "workload": wl, "op": "fwd+dlhs+drhs (6*M*K*N)", "ms": ms,
+                      "flops": flops, "algorithmic_bytes": byts, "tflops": rl["tflops"], "gbs": rl["gbs"],
+                      "roofline": rl})
+  return entries
+
+
+def run_single(args, w, peaks):
+  """One kernel alone on one workload (profiler runs and tuning)."""
+  from tokamax_b200 import _capi
+  dev = torch.device("cuda", 0)
+  torch.cuda.set_device(dev)
+  _capi.load()
+  step, alg_bytes, cfg_repr, keep = build_kernel_step(w, args.op, dev, args.fp8_path)
   for _ in range(max(args.warmup, 3)):
     step()
-  torch.cuda.synchronize()
-  with ClockSampler(physical_gpu_index(0)) as clocks:
-    start = torch.cuda.Event(enable_timing=True)
-    end = torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    start.record(stream)
-    for _ in range(args.steps):
-      step()
-    end.record(stream)
-    torch.cuda.synchronize()
-    total_ms = start.elapsed_time(end)
-    # keep the sampler alive long enough to see the region when it is very short
-    if total_ms < 400:
-      t_end = time.time() + 0.5
-      while time.time() < t_end:
-        step()
-      torch.cuda.synchronize()
+  ms, launches, clocks = time_region(step, torch.cuda.current_stream(), args.steps, gpu_id_for_smi(0),
+                                     min_region_ms=0.0 if args.kernel_only else 450.0)
   _capi.device_status()
-  ms = total_ms / args.steps
-  tflops = w.flops / (ms * 1e-3) / 1e12
-
-  if args.kernel_only:
-    return {"metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
-            "ms_per_step": ms, "config": {"workload": w.name, "op": args.op, "kernel_config": repr(cfg)},
-            "kernel_only": True, "gpu_launches": args.steps, "clocks": clocks.summary(),
-            "roofline": {"bound": bound_kind, "tflops": tflops, "gbs": alg_bytes / (ms * 1e-3) / 1e9,
-                         "frac_tensor": tflops / peaks["bf16"], "frac_hbm": alg_bytes / (ms * 1e-3) / 1e9 / peaks["hbm"]}}
-  if args.op != "fwd" or quant:
-    raise SystemExit("the full line (e2e, cpu baseline) is defined for the bf16 forward; use --kernel-only")
-
-  # End to end through the public API with host buffers.
-  h_lhs = lhs.cpu().pin_memory()
-  h_rhs = rhs.cpu().pin_memory()
-  h_gs = gs.cpu().pin_memory()
-  h_out = torch.empty(w.m, w.n, dtype=torch.bfloat16).pin_memory()
-  # The public host-buffer call: every step copies this step's operands from pinned host
-  # memory, multiplies, and copies the result back, pipelined by groups over three streams.
-  del lhs, rhs, out
-  torch.cuda.empty_cache()
-  host_op = tk.HostRaggedDot(dev)
-
-  def e2e_step():
-    host_op(h_lhs, h_rhs, h_gs, out=h_out)
-
-  e2e_steps = args.steps
-  for _ in range(2):
-    e2e_step()
-  torch.cuda.synchronize()
-  s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  s2.record(stream)
-  for _ in range(e2e_steps):
-    e2e_step()
-  e2.record(stream)
-  torch.cuda.synchronize()
-  e2e_ms = s2.elapsed_time(e2) / e2e_steps
-  h2d = h_lhs.numel() * 2 + h_rhs.numel() * 2 + h_gs.numel() * 4
-  d2h = h_out.numel() * 2
-  del h_lhs, h_rhs, h_out, host_op
-
-  threads = os.cpu_count() or 1
-  cpu_tf, cpu_desc, _ = cpu_grouped_gemm_sample(w, 12.0, threads)
-
-  # The multi-GPU runs time the expert-parallel layer, a different workload from this line's.
-  # Its single-GPU figure is measured here too so that a like-for-like scaling baseline exists.
-  ep_line = None
-  if w.name == "cfg2" and not args.kernel_only:
-    torch.cuda.empty_cache()
-    ep_args = argparse.Namespace(**{**vars(args), "steps": max(3, min(args.steps, 10))})
-    ep = run_expert_parallel(ep_args, peaks, 1, 0, 0)
-    ep_line = {"workload": "ep", "n_gpus": 1, "value": ep["value"], "unit": UNIT, "ms_per_step": ep["ms_per_step"]}
-
-  line = {
-      "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
-      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-      "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-      "config": {"workload": w.name, "note": w.note, "m": w.m, "k": w.k, "n": w.n, "g": w.g,
-                 "op": "forward", "kernel_config": repr(cfg), "l2": "inputs_exceed_l2 (1.07 GB vs 126 MB), no flush"},
-      "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["bf16"], "unit": UNIT,
-                   "frac": tflops / peaks["bf16"], "traffic": NCU_TRAFFIC_BYTES.get(w.name),
-                   "peak_source": peaks["source"] + ", bf16 burst",
-                   "algorithmic_flops_per_launch": w.flops,
-                   "algorithmic_bytes_per_launch": float(alg_bytes)},
-      "cpu_baseline": {"value": cpu_tf, "unit": UNIT, "cores": threads, "kind": "port", "sample": cpu_desc},
-      "e2e": {"value": w.flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
-              "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-      "gpu_launches": args.steps,
-      "clocks": clocks.summary(),
-      "scaling_baseline": ep_line,
-  }
-  return line
+  rl = roofline_entry(w.flops, alg_bytes, ms, peaks, peaks["bf16"])
+  return {"metric": METRIC, "value": rl["tflops"], "unit": UNIT, "n_gpus": 1, "steps": launches,
+          "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16",
+          "data": "synthetic",
+          "config": {"workload": w.name, "op": args.op, "kernel_config": cfg_repr, "m": w.m, "k": w.k, "n": w.n,
+                     "g": w.g},
+          "kernel_only": True, "gpu_launches": launches, "clocks": clocks, "roofline": rl}
 
 
 # ----------------------------------------------------------------------------- expert parallel
 EP_TOKENS, EP_K, EP_N, EP_G, EP_TOPK = 8192, 7168, 2048, 256, 8
 
 
+def ep_config(world: int, exchange: str, chunks: int) -> dict:
+  """The `config` object of the line: identical in the GPU arm and the reference arm."""
+  return {"workload": "ep",
+          "note": "expert-parallel MoE layer: route, dispatch rows to the experts' owners, grouped GEMM, "
+                  "return rows, gate-weighted combine",
+          "tokens_per_rank": EP_TOKENS, "k": EP_K, "n": EP_N, "experts": EP_G, "top_k": EP_TOPK,
+          "parallelism": f"ep{world}", "l2": "inputs_exceed_l2, no flush"}
+
+
+def ep_routing(rank: int):
+  from tokamax_b200.ragged_dot import arg_specs
+  return arg_specs.topk_routing(EP_TOKENS, EP_G, EP_TOPK, seed=10_000 + rank)
+
+
+def ep_parity_check(layer, tokens, ids, gates, y, plan, rhs, world, rank, dev, samples_per_rank=4):
+  """Sampled tokens of every rank against a dense top-k MoE recomputed on the host by the CPU
+  oracle (each rank contributes the experts it owns), and this rank's group sizes against the
+  global histogram of all ranks' routing.  Returns (checked tokens, max abs err, worst err /
+  tolerance, group sizes exact)."""
+  import torch.distributed as dist
+  from oracle import ragged_dot_ref as ref   # the checker
+  gl = EP_G // world
+  # group bookkeeping: exact against the histogram of every rank's (seeded) routing
+  want = np.zeros(EP_G, np.int64)
+  for r in range(world):
+    want += np.bincount(ep_routing(r)[0].reshape(-1), minlength=EP_G)
+  got = plan.group_sizes.cpu().numpy().astype(np.int64)
+  gs_exact = bool(np.array_equal(got, want[rank * gl:(rank + 1) * gl]))
+
+  s = samples_per_rank
+  pick = torch.from_numpy(np.random.default_rng(77 + rank).choice(EP_TOKENS, s, replace=False)).to(dev)
+  mine = dict(tok=tokens[pick].contiguous(), ids=ids[pick].to(torch.int32).contiguous(),
+              gates=gates[pick].to(torch.float32).contiguous(), y=y[pick].contiguous())
+  gathered = {}
+  for k_, v in mine.items():
+    if world > 1:
+      bufs = [torch.empty_like(v) for _ in range(world)]
+      dist.all_gather(bufs, v)
+      gathered[k_] = torch.cat(bufs).cpu()
+    else:
+      gathered[k_] = v.cpu()
+  n_tok = gathered["tok"].shape[0]
+  partial = torch.zeros(n_tok, EP_N, dtype=torch.float64)
+  for t in range(n_tok):
+    for j in range(EP_TOPK):
+      e = int(gathered["ids"][t, j])
+      if e // gl != rank:
+        continue
+      w_e = rhs[e - rank * gl].cpu()[None]                         # [1, K, N] bf16, this rank's expert
+      row = ref.ragged_dot_ref(gathered["tok"][t:t + 1], w_e, np.array([1]))   # bf16 [1, N]
+      partial[t] += float(gathered["gates"][t, j]) * row[0].double()
+  partial = partial.to(dev)
+  if world > 1:
+    dist.all_reduce(partial)
+  want_y = partial.cpu()
+  got_y = gathered["y"].double()
+  err = (got_y - want_y).abs()
+  tol = 2e-2 + 2e-2 * want_y.abs()
+  return n_tok, float(err.max()), float((err / tol).max()), gs_exact
+
+
+def cpu_ep_layer(threads: int, target_seconds: float):
+  """The layer's per-rank work on the host cores by the CPU restatement: stable sort of the
+  (token, expert) pairs, row gather, per-expert float32 matmul of bf16 inputs (the oracle),
+  gate-weighted combine.  Rank 0's routing and token count; eight weight slabs are cycled
+  over the 256 experts so that the host needs 235 MB of weights, not 7.5 GB.  Repeated until
+  `target_seconds` have passed.  Returns (TFLOP/s, description, seconds per pass)."""
+  from oracle import ragged_dot_ref as ref  # the checker, used here as the timed CPU baseline
+  torch.set_num_threads(threads)
+  rng = np.random.default_rng(0)
+  ids, gates = ep_routing(0)
+  tokens = torch.from_numpy(rng.standard_normal((EP_TOKENS, EP_K), dtype=np.float32)).bfloat16()
+  slabs = [torch.from_numpy(rng.standard_normal((1, EP_K, EP_N), dtype=np.float32) * EP_K ** -0.5).bfloat16()
+           for _ in range(8)]
+  gates_t = torch.from_numpy(gates)
+
+  def one_pass():
+    t0 = time.perf_counter()
+    flat = ids.reshape(-1)
+    order = np.argsort(flat, kind="stable")
+    counts = np.bincount(flat, minlength=EP_G)
+    rows = tokens[torch.from_numpy(order // EP_TOPK)]
+    out = torch.empty(rows.shape[0], EP_N, dtype=torch.bfloat16)
+    off = 0
+    for e in range(EP_G):
+      c = int(counts[e])
+      if c:
+        out[off:off + c] = ref.ragged_dot_ref(rows[off:off + c], slabs[e % 8], np.array([c]))
+        off += c
+    y = torch.zeros(EP_TOKENS, EP_N, dtype=torch.float32)
+    y.index_add_(0, torch.from_numpy(order // EP_TOPK), out.float() * gates_t.reshape(-1)[torch.from_numpy(order)][:, None])
+    y = y.bfloat16()
+    return time.perf_counter() - t0
+
+  one_pass()  # warm-up
+  times = []
+  t_begin = time.perf_counter()
+  while not times or time.perf_counter() - t_begin < target_seconds:
+    times.append(one_pass())
+  t = float(np.median(times))
+  flops = 2.0 * EP_TOKENS * EP_TOPK * EP_K * EP_N
+  desc = (f"ep: one rank's whole step ({EP_TOKENS} tokens x top-{EP_TOPK}, {EP_TOKENS * EP_TOPK} rows over "
+          f"{EP_G} experts: sort, gather, per-expert float32 matmul of bf16 inputs, combine), "
+          f"{len(times)} passes, {threads} threads")
+  return flops / t / 1e12, desc, t
+
+
+def run_reference_arm(args, world, rank):
+  if rank != 0:
+    return None
+  threads = os.cpu_count() or 1
+  vals = []
+  desc = ""
+  for i in range(args.warmup + args.steps):
+    tf, desc, t = cpu_ep_layer(threads, 0.0)   # one pass per step
+    if i >= args.warmup:
+      vals.append((tf, t))
+    if i >= args.warmup and sum(v[1] for v in vals) > 150.0:
+      break
+  tf = float(np.median([v[0] for v in vals]))
+  ms = float(np.mean([v[1] for v in vals]) * 1e3)
+  cfg = ep_config(world, "", 0)
+  cfg["reference_path"] = "CPU restatement of implementation='xla' (jax not installable here), one rank's step"
+  return {
+      "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus,
+      "steps": len(vals), "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+      "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
+      "cpu_baseline": {"value": tf, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+      "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+      "gpu_launches": 0,
+  }
+
+
 def run_expert_parallel(args, peaks, world, rank, local_rank):
   import torch.distributed as dist
   from tokamax_b200 import _capi
   from tokamax_b200.expert_parallel import ExpertParallelMoE
-  from tokamax_b200.ragged_dot import arg_specs
 
   dev = torch.device("cuda", local_rank)
   torch.cuda.set_device(dev)
@@ -386,40 +493,47 @@ def run_expert_parallel(args, peaks, world, rank, local_rank):
     rhs[i] = (torch.randn(EP_K, EP_N, device=dev, generator=gen, dtype=torch.float32) * EP_K ** -0.5).to(torch.bfloat16)
   gen = torch.Generator(device=dev).manual_seed(rank)
   tokens = torch.randn(EP_TOKENS, EP_K, device=dev, generator=gen, dtype=torch.float32).to(torch.bfloat16)
-  ids_np, gates_np = arg_specs.topk_routing(EP_TOKENS, EP_G, EP_TOPK, seed=10_000 + rank)
+  ids_np, gates_np = ep_routing(rank)
   ids = torch.from_numpy(ids_np).to(dev)
   gates = torch.from_numpy(gates_np).to(dev)
-  # Chunks of local experts whose exchanges overlap the neighbouring GEMMs: 8 measured best on
-  # 8 GPUs (3.09 ms against 3.31 ms unchunked), 4 on 2 and 4 GPUs.
-  num_chunks = args.ep_chunks if args.ep_chunks > 0 else (8 if world >= 8 else 4)
-  layer = ExpertParallelMoE(rhs, EP_G, num_chunks=num_chunks, exchange=args.ep_exchange)
+  layer = ExpertParallelMoE(rhs, EP_G, num_chunks=args.ep_chunks if args.ep_chunks > 0 else 4,
+                            exchange=args.ep_exchange)
   stream = torch.cuda.current_stream()
+  sampler_id = gpu_id_for_smi(local_rank)
 
   def barrier():
     if world > 1:
       dist.barrier()
     torch.cuda.synchronize()
 
-  rows_seen = 0
-  for _ in range(max(args.warmup, 3)):
-    _, plan = layer(tokens, ids, gates)
+  warmup = max(args.warmup, 3)
+  for _ in range(warmup):
+    y, plan = layer(tokens, ids, gates)
   barrier()
-  with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+  layer.gemm_events = []          # (start, end) CUDA events around the grouped-GEMM launch of each step
+  with ClockSampler(sampler_id) as clocks:
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     start.record(stream)
     for _ in range(args.steps):
-      _, plan = layer(tokens, ids, gates)
-      rows_seen += EP_TOKENS * EP_TOPK  # rows this rank routed; summed over ranks = rows multiplied
+      y, plan = layer(tokens, ids, gates)
     end.record(stream)
     barrier()
     total_ms = start.elapsed_time(end)
+    gemm_ms = [s.elapsed_time(e) for s, e in layer.gemm_events]
+    layer.gemm_events = None
+    launches_per_step = layer.launches_last_call
     # keep the same work running until the 100 ms clock sampler has seen it
     t_end = time.time() + 0.6
     while time.time() < t_end:
       layer(tokens, ids, gates)
     barrier()
   _capi.device_status()
+  layer.check_overflow()
+  rows_local = int(plan.group_sizes.sum().item())     # rows this rank multiplied per step
+
+  # parity on the result of the last timed step
+  checked, max_err, worst_ratio, gs_exact = ep_parity_check(layer, tokens, ids, gates, y, plan, rhs, world, rank, dev)
 
   # end to end: host tokens / routing in, combined activations out
   h_tok, h_ids, h_gates = tokens.cpu().pin_memory(), ids.cpu().pin_memory(), gates.cpu().pin_memory()
@@ -430,8 +544,8 @@ def run_expert_parallel(args, peaks, world, rank, local_rank):
     d_tok.copy_(h_tok, non_blocking=True)
     d_ids.copy_(h_ids, non_blocking=True)
     d_gates.copy_(h_gates, non_blocking=True)
-    y, _ = layer(d_tok, d_ids, d_gates)
-    h_out.copy_(y, non_blocking=True)
+    yy, _ = layer(d_tok, d_ids, d_gates)
+    h_out.copy_(yy, non_blocking=True)
 
   for _ in range(2):
     e2e_step()
@@ -444,42 +558,59 @@ def run_expert_parallel(args, peaks, world, rank, local_rank):
   barrier()
   e2e_total = s2.elapsed_time(e2)
 
-  stats = torch.tensor([total_ms, e2e_total, float(rows_seen)], device=dev, dtype=torch.float64)
-  mx = stats.clone()
-  sm = stats.clone()
+  gemm_mean = float(np.mean(gemm_ms)) if gemm_ms else 0.0
+  stats = torch.tensor([total_ms, e2e_total, gemm_mean, max_err, worst_ratio, 0.0 if gs_exact else 1.0],
+                       device=dev, dtype=torch.float64)
+  sums = torch.tensor([float(rows_local), float(checked) / world], device=dev, dtype=torch.float64)
   if world > 1:
-    dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-    dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+  parity_ok = float(stats[4]) <= 1.0 and float(stats[5]) == 0.0
   if rank != 0:
-    return None
-  total_rows = float(sm[2])
-  flops_total = 2.0 * total_rows * EP_K * EP_N            # all ranks, all timed steps
-  ms = float(mx[0]) / args.steps
-  tflops = flops_total / (float(mx[0]) * 1e-3) / 1e12
-  e2e_tflops = flops_total / (float(mx[1]) * 1e-3) / 1e12
-  per_gpu = tflops / world
+    return None, parity_ok
+  rows_step = float(sums[0])                               # all ranks, one step
+  flops_step = 2.0 * rows_step * EP_K * EP_N
+  ms = float(stats[0]) / args.steps
+  tflops = flops_step / (ms * 1e-3) / 1e12
+  e2e_ms = float(stats[1]) / args.steps
+  # Roofline of the dominant kernel (the grouped GEMM of one rank): algorithmic bytes = received rows
+  # read once + this rank's expert weights read once + output rows written once.
+  rows_rank = rows_step / world
+  g_flops = 2.0 * rows_rank * EP_K * EP_N
+  g_bytes = rows_rank * EP_K * 2 + gl * EP_K * EP_N * 2 + rows_rank * EP_N * 2
+  g_ms = float(stats[2])
+  peak_tf = peaks["bf16_sustained"]                        # a kernel timed inside a long step
+  rl = roofline_entry(g_flops, g_bytes, g_ms, peaks, peak_tf) if g_ms > 0 else None
+  if rl is not None:
+    hbm = rl["bound"] == "hbm"
+    roofline = {"bound": rl["bound"], "achieved": rl["gbs"] if hbm else rl["tflops"],
+                "peak": peaks["hbm"] if hbm else peak_tf, "unit": "GB/s" if hbm else UNIT,
+                "frac": rl["frac"], "traffic": None, "kernel": layer.gemm_kernel_name,
+                "ms_per_launch": g_ms, "algorithmic_flops_per_launch": g_flops,
+                "algorithmic_bytes_per_launch": g_bytes, "frac_tensor": rl["frac_tensor"],
+                "frac_hbm": rl["frac_hbm"],
+                "peak_source": peaks["source"] + (", HBM copy" if hbm else ", bf16 sustained (kernel timed inside a long step)")}
+  else:
+    roofline = None
+  cfg = ep_config(world, layer.exchange, layer.num_chunks)
+  cfg.update({"exchange": layer.exchange_name, "rows_per_step": rows_step})
   line = {
       "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-      "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-      "config": {"workload": "ep", "note": "expert-parallel MoE layer: dispatch all-to-all, grouped GEMM, combine all-to-all",
-                 "tokens_per_rank": EP_TOKENS, "k": EP_K, "n": EP_N, "experts": EP_G, "top_k": EP_TOPK,
-                 "parallelism": f"ep{world}", "exchange": layer.exchange if world > 1 else "local",
-                 "overlap_chunks": layer.num_chunks if world > 1 else 1,
-                 "l2": "inputs_exceed_l2, no flush"},
-      "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_sustained"], "unit": UNIT,
-                   "frac": per_gpu / peaks["bf16_sustained"], "traffic": None,
-                   "peak_source": peaks["source"] + ", bf16 sustained (kernel timed inside a long step); per GPU, whole layer time"},
-      "e2e": {"value": e2e_tflops, "unit": UNIT,
+      "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+      "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
+      "roofline": roofline,
+      "parity": {"checked": int(round(float(sums[1]) * world)) if world > 1 else checked,
+                 "max_abs_err": float(stats[3]), "worst_err_over_tolerance": float(stats[4]),
+                 "tolerance": "2e-2 + 2e-2*|x| against the CPU oracle (dense top-k MoE on sampled tokens)",
+                 "group_sizes_exact": float(stats[5]) == 0.0, "ok": parity_ok},
+      "e2e": {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
               "h2d_bytes_per_step": world * (h_tok.numel() * 2 + h_ids.numel() * 4 + h_gates.numel() * 4),
-              "d2h_bytes_per_step": world * h_out.numel() * 2, "ms_per_step": float(mx[1]) / args.steps},
-      # own kernels per step.  p2p: 3 sort + counts scatter + per chunk (row scatter, grouped
-      # GEMM, scatter back) + combine;  nccl / local: 3 sort + gather + GEMM per chunk + combine
-      "gpu_launches": args.steps * (5 + 3 * layer.num_chunks if (world > 1 and layer.exchange == "p2p")
-                                    else 5 + (layer.num_chunks if world > 1 else 1)),
+              "d2h_bytes_per_step": world * h_out.numel() * 2, "ms_per_step": e2e_ms},
+      "gpu_launches": args.steps * launches_per_step,
+      "gpu_launches_per_step": launches_per_step,
       "clocks": clocks.summary(),
   }
-  return line
+  return line, parity_ok
 
 
 def _claim_stdout():
@@ -505,14 +636,17 @@ def main():
   ap.add_argument("--workload", default=None, choices=[None, "cfg1", "cfg2", "cfg3", "cfg4", "dsv3", "ep"])
   ap.add_argument("--op", default="fwd", choices=["fwd", "dlhs", "drhs"],
                   help="which contraction of the workload to time (single GPU)")
+  ap.add_argument("--rhs-dtype", default=None, choices=[None, "fp8", "int8", "bf16"],
+                  help="weight type of a single-kernel run (cfg3 defaults to fp8)")
   ap.add_argument("--groups", type=int, default=0,
                   help="keep only the first N groups of the workload (smaller profiler captures)")
-  ap.add_argument("--ep-exchange", default=None, choices=[None, "p2p", "nccl"],
-                  help="row exchange of the expert-parallel layer (default: p2p on more than one GPU)")
+  ap.add_argument("--ep-exchange", default=None, choices=[None, "fused", "p2p", "nccl"],
+                  help="row exchange of the expert-parallel layer (default: the fused kernel)")
   ap.add_argument("--ep-chunks", type=int, default=0,
-                  help="expert chunks whose exchanges overlap the neighbouring GEMMs (N > 1); 0 = 8 on 8 GPUs, else 4")
+                  help="expert chunks of the p2p / nccl exchanges whose transfers overlap the neighbouring GEMMs")
   ap.add_argument("--kernel-only", action="store_true",
-                  help="time the resident-input region only (no e2e, no CPU baseline): for profiler runs")
+                  help="exactly --steps launches of the timed region, no padding for the clock sampler")
+  ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel suite of the N = 1 line")
   args = ap.parse_args()
 
   world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -520,39 +654,46 @@ def main():
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
   from tokamax_b200.ragged_dot import arg_specs
 
-  workload = args.workload or ("cfg2" if max(world, args.gpus) == 1 else "ep")
-  if workload == "ep":
-    w = arg_specs.Workload("ep", EP_TOKENS * EP_TOPK, EP_K, EP_N, EP_G // max(world, 1),
-                           tuple([EP_TOKENS * EP_TOPK // (EP_G // max(world, 1))] * (EP_G // max(world, 1))),
-                           note="local grouped GEMM of the expert-parallel layer (mean group sizes)")
-  else:
-    w = arg_specs.workload(workload)
-    if args.groups and args.groups < w.g:
-      gs = tuple(w.group_sizes[:args.groups])
-      w = dataclasses.replace(w, name=f"{w.name}[:{args.groups}]", g=args.groups, group_sizes=gs, m=sum(gs))
-
+  workload = args.workload or "ep"
   if args.impl == "reference":
-    line = run_reference_arm(args, w, world, rank)
+    line = run_reference_arm(args, world, rank)
     if line is not None:
       print(json.dumps(line), file=json_out, flush=True)
     return
 
   peaks = load_peaks()
-  if world > 1:
-    import torch.distributed as dist
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    torch.cuda.set_device(local_rank)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    try:
-      line = run_expert_parallel(args, peaks, world, rank, local_rank)
-    finally:
-      dist.destroy_process_group()
-  elif workload == "ep":
-    line = run_expert_parallel(args, peaks, 1, 0, 0)
+  ok = True
+  if workload == "ep":
+    if world > 1:
+      import torch.distributed as dist
+      os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+      torch.cuda.set_device(local_rank)
+      dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+      try:
+        line, ok = run_expert_parallel(args, peaks, world, rank, local_rank)
+      finally:
+        dist.destroy_process_group()
+    else:
+      line, ok = run_expert_parallel(args, peaks, 1, 0, 0)
+      torch.cuda.empty_cache()
+      threads = os.cpu_count() or 1
+      cpu_tf, cpu_desc, _ = cpu_ep_layer(threads, 2.0 if args.no_kernels else 12.0)
+      line["cpu_baseline"] = {"value": cpu_tf, "unit": UNIT, "cores": threads, "kind": "port", "sample": cpu_desc}
+      if not args.no_kernels:
+        line["kernels"] = run_kernel_suite(torch.device("cuda", 0), peaks, gpu_id_for_smi(0))
   else:
+    w = arg_specs.workload(workload)
+    if args.rhs_dtype is not None:
+      w = dataclasses.replace(w, rhs_dtype={"fp8": torch.float8_e4m3fn, "int8": torch.int8,
+                                            "bf16": torch.bfloat16}[args.rhs_dtype])
+    if args.groups and args.groups < w.g:
+      gs = tuple(w.group_sizes[:args.groups])
+      w = dataclasses.replace(w, name=f"{w.name}[:{args.groups}]", g=args.groups, group_sizes=gs, m=sum(gs))
     line = run_single(args, w, peaks)
   if line is not None:
     print(json.dumps(line), file=json_out, flush=True)
+  if not ok:
+    sys.exit(3)
 
 
 if __name__ == "__main__":

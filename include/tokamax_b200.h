@@ -36,7 +36,10 @@ typedef enum tkmx_status {
   TKMX_ERR_CUDA = 4,             /* a CUDA runtime / driver call failed; see tkmx_last_cuda_error */
   TKMX_ERR_WORKSPACE = 5,        /* workspace smaller than tkmx_ragged_dot_workspace_bytes says */
   TKMX_ERR_DEVICE_TIMEOUT = 6,   /* reported by tkmx_device_status: a bounded wait in a kernel gave up */
-  TKMX_ERR_TOO_LARGE = 7         /* size beyond a stated static limit */
+  TKMX_ERR_TOO_LARGE = 7,        /* size beyond a stated static limit */
+  TKMX_ERR_DEVICE_STATE = 8      /* reported by tkmx_device_status: a kernel stopped early because its
+                                    bookkeeping was inconsistent (tile-counter word shared by two
+                                    launches in flight; expert-parallel row outside a receive buffer) */
 } tkmx_status;
 
 typedef enum tkmx_dtype {
@@ -256,19 +259,69 @@ TKMX_API int tkmx_moe_gather_rows(const void* src, const int32_t* pos, void* dst
                                   int32_t top_k, int64_t row_bytes, void* cuda_stream);
 
 /*
- * Row scatter into peer GPUs' buffers over NVLink (peer-mapped pointers, plain stores):
- * row i of src (row src_row[i] if src_row != NULL) goes to row dst_row[i] of the buffer whose
- * base address is peer_base[dst_peer[i]]; dst_peer[i] < 0 skips the row.  peer_base is a
- * DEVICE array of addresses.  Rows aimed outside [0, capacity_rows) are dropped and
- * *overflow_flag (device int32) is set to 1.  The caller orders this against the readers of
- * the destination buffers (a cross-rank barrier on the stream).  No reference counterpart:
- * it replaces the all-to-all a caller of the reference would run between ragged_gather and
- * ragged_dot.
+ * tkmx_moe_sort_pairs that also returns the inverse permutation: sorted_pair[pos[p]] = p for
+ * every pair with pos[p] >= 0 (int32[num_pairs]; entries past the number of valid pairs are
+ * not written; NULL = not wanted).  The row order the expert-parallel kernel sends in.
  */
-TKMX_API int tkmx_moe_scatter_rows_p2p(const void* src, const int32_t* src_row, const int32_t* dst_peer,
-                                       const int32_t* dst_row, const uint64_t* peer_base,
-                                       int64_t num_rows, int64_t row_bytes, int64_t capacity_rows,
-                                       int32_t* overflow_flag, void* cuda_stream);
+TKMX_API int tkmx_moe_sort_pairs_inverse(const int32_t* expert_ids, int64_t num_pairs, int32_t num_experts,
+                                         int32_t* pos, int32_t* sorted_pair, int32_t* expert_counts,
+                                         void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
+ * Expert-parallel MoE layer over peer-mapped GPU memory (one process per GPU on one NVLink /
+ * NVSwitch domain).  No reference counterpart: upstream leaves sharding to the caller's
+ * shard_map and only offers `group_offset` / `num_actual_groups`
+ * (tokamax/_src/ops/ragged_dot/pallas_mosaic_tpu_v2.py:89-93); these entry points replace the
+ * all-to-all + ragged_gather + ragged_dot + all-to-all + ragged_gather_reduce sequence such a
+ * caller writes.  Experts are sharded contiguously, rank r owning [r * G/W, (r + 1) * G/W).
+ *
+ * Buffers every rank allocates in memory its peers can address, with the same sizes everywhere:
+ *   recv     [capacity_rows, k]  token rows this rank's experts receive, (local expert, source) order
+ *   arrive   uint32[G/W]         rows arrived per local expert
+ *   ret      [T * top_k, n]      this rank's pairs' output rows in expert-sorted order
+ *   counts   int32[W, G]         every rank's per-expert pair counts
+ *   flags    uint32[W]           barrier flags, zero before the first call
+ * peer_table is a DEVICE array uint64[5][16]: entry [t][r] = address of buffer t (0 recv,
+ * 1 arrive, 2 ret, 3 counts, 4 flags) of rank r as mapped into this process.  W <= 16, G <= 1024.
+ *
+ * One step on every rank, all on one stream:
+ *   tkmx_moe_sort_pairs_inverse -> tkmx_ep_exchange_plan -> tkmx_ep_moe_fused
+ *   -> tkmx_cross_rank_barrier -> tkmx_moe_combine(ret, pos, gates)
+ *
+ * Every cross-rank wait is bounded: a flag wait gives up after timeout_ns, a wait for rows after
+ * 2 s; the kernel then records a code (tkmx_device_status returns TKMX_ERR_DEVICE_TIMEOUT) and
+ * returns, leaving the context usable.  `sequence` must grow by one per barrier call, the same
+ * on every rank (tkmx_ep_exchange_plan contains one barrier).
+ */
+TKMX_API size_t tkmx_ep_plan_bytes(int32_t num_experts, int32_t world);
+
+/* Pushes my_counts (int32[G], from the sort) into row `rank` of every rank's counts matrix,
+ * zeroes this rank's arrival counters, passes the flag barrier (which also orders this step
+ * after every rank's previous one), and fills `plan` (tkmx_ep_plan_bytes) from the complete
+ * matrix.  One CTA. */
+TKMX_API int tkmx_ep_exchange_plan(const int32_t* my_counts, const uint64_t* peer_table,
+                                   int32_t* counts_all_local, uint32_t* flags_local, uint32_t* arrive_local,
+                                   int32_t* plan, int32_t num_experts, int32_t world, int32_t rank,
+                                   uint32_t sequence, int64_t timeout_ns, void* cuda_stream);
+
+/* The fused kernel: while two warps of every CTA copy this rank's token rows (tokens
+ * [num_tokens, k], order given by sorted_pair and plan) into the owners' recv buffers and bump
+ * their arrival counters, the other warps multiply the rows that have arrived in recv_local by
+ * rhs_local [G/W, k, n] (tcgen05 / TMEM / TMA pipeline of tkmx_ragged_dot_fwd) and store every
+ * finished row into its source rank's ret buffer.  phases: 1 = send only, 2 = multiply and
+ * return only (everything must have arrived), 3 = both (the product form).  dtype BF16 or F16;
+ * k and n multiples of 8.  Only config->collective, num_stages, grid_* and max_ctas are used. */
+TKMX_API int tkmx_ep_moe_fused(const void* tokens, const int32_t* sorted_pair, const void* recv_local,
+                               const void* rhs_local, const int32_t* plan, const uint64_t* peer_table,
+                               const uint32_t* arrive_local, int64_t num_tokens, int32_t top_k, int64_t k,
+                               int64_t n, int32_t num_experts, int32_t world, int32_t rank,
+                               int64_t capacity_rows, int dtype, int phases, const tkmx_config* config,
+                               void* cuda_stream);
+
+/* Flag barrier across the ranks on the stream (one warp): all earlier work of this stream on
+ * every rank is complete and visible when the kernel ends. */
+TKMX_API int tkmx_cross_rank_barrier(const uint64_t* peer_table, uint32_t* flags_local, int32_t world,
+                                     int32_t rank, uint32_t sequence, int64_t timeout_ns, void* cuda_stream);
 
 /*
  * y[t, :] = sum_k gates[t, k] * rows[pos[t * top_k + k], :], accumulated in float32 in

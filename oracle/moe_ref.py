@@ -97,3 +97,31 @@ def cyclic_ragged_dot_ref(rows: torch.Tensor, rhs: torch.Tensor, segment_sizes, 
   g = rhs.shape[0]
   expanded = rhs[[i % g for i in range(len(seg))]]
   return ref.ragged_dot_ref(rows, expanded, seg, out_dtype=out_dtype)
+
+
+def ep_plan_ref(counts_all: np.ndarray, rank: int) -> dict:
+  """Offsets of one expert-parallel step as rank `rank` derives them from the all-gathered
+  per-expert pair counts `counts_all` int [W, G] (experts sharded contiguously, G/W per rank).
+  This layer has no counterpart in the reference; the layout it restates is the one declared in
+  include/tokamax_b200.h: a rank's receive buffer is ordered (local expert, source rank), its
+  return buffer holds its own pairs in expert-sorted order, rows are sent local-expert major.
+  Returns the tables of the device plan under their names."""
+  c = np.maximum(np.asarray(counts_all).astype(np.int64), 0)
+  w, g = c.shape
+  gl = g // w
+  send_off_all = np.cumsum(c, 1) - c                       # [src, e]: src's first sorted position of e
+  within = np.cumsum(c, 0) - c                             # [src, e]: rows of earlier sources, same expert
+  per_expert = c.sum(0)                                    # [e]
+  pe = per_expert.reshape(w, gl)
+  expert_start = (np.cumsum(pe, 1) - pe).reshape(-1)       # first row of e in its owner's receive buffer
+  mine = slice(rank * gl, (rank + 1) * gl)
+  seg_start = np.empty((gl, w + 1), np.int64)
+  seg_start[:, :w] = (expert_start[mine][None, :] + within[:, mine]).T
+  seg_start[:, w] = expert_start[mine] + per_expert[mine]
+  ret_off = send_off_all[:, mine].T                        # [local e, src]
+  v_to_e = np.array([(v % w) * gl + v // w for v in range(g)])
+  vcount = c[rank][v_to_e]
+  vstart = np.concatenate([[0], np.cumsum(vcount)])
+  i32 = lambda a: np.asarray(a, np.int32)
+  return dict(group_sizes=i32(per_expert[mine]), vstart=i32(vstart), src_off=i32(send_off_all[rank][v_to_e]),
+              dst_row=i32((expert_start + within[rank])[v_to_e]), seg_start=i32(seg_start), ret_off=i32(ret_off))

@@ -1,5 +1,6 @@
-"""Expert-parallel layer on 2 real GPUs (NCCL): result equals a dense top-k MoE, received
-group sizes equal the global histogram slice.  Skipped on boxes with fewer than 2 GPUs."""
+"""Expert-parallel layer on 2 and 4 real GPUs: result equals a dense top-k MoE, received group
+sizes equal the global histogram slice.  Both exchanges: the fused kernel over peer-mapped
+memory and the NCCL all-to-all form.  Skipped on boxes with fewer GPUs."""
 
 import os
 import socket
@@ -39,13 +40,15 @@ def _worker(rank, world, port, q, chunks, exchange):
     layer = ExpertParallelMoE(rhs[rank * gl:(rank + 1) * gl].cuda(), G, num_chunks=chunks, exchange=exchange)
     tok, ids, gates = per_rank[rank]
     y, plan = layer(tok.cuda(), ids.cuda(), gates.cuda())
+    y = y.clone()
+    gs_first = plan.group_sizes.clone()
     y2, _ = layer(tok.cuda(), ids.cuda(), gates.cuda())   # buffers are reused call after call
     torch.cuda.synchronize()
     assert torch.equal(y, y2)
-    _capi.device_status()
+    layer.check_overflow()      # no timed-out wait, no dropped row
     all_ids = torch.cat([p[1].reshape(-1) for p in per_rank])
     want_gs = torch.bincount(all_ids.long(), minlength=G)[rank * gl:(rank + 1) * gl]
-    ok_gs = torch.equal(plan.group_sizes.cpu().long(), want_gs)
+    ok_gs = torch.equal(gs_first.cpu().long(), want_gs)
     want = torch.zeros(T, N)
     for j in range(TOPK):
       w = rhs[ids[:, j].long()].float()
@@ -56,19 +59,20 @@ def _worker(rank, world, port, q, chunks, exchange):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("chunks,exchange", [(1, "nccl"), (4, "nccl"), (1, "p2p"), (4, "p2p")])
-def test_two_gpu_expert_parallel_matches_dense_moe(chunks, exchange):
-  if torch.cuda.device_count() < 2:
-    pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world,chunks,exchange", [(2, 1, "nccl"), (2, 4, "nccl"), (2, 1, "fused"), (4, 1, "fused"),
+                                                   (4, 2, "nccl")])
+def test_multi_gpu_expert_parallel_matches_dense_moe(world, chunks, exchange):
+  if torch.cuda.device_count() < world:
+    pytest.skip(f"needs {world} GPUs")
   with socket.socket() as s:
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
   ctx = mp.get_context("spawn")
   q = ctx.Queue()
-  procs = [ctx.Process(target=_worker, args=(r, 2, port, q, chunks, exchange)) for r in range(2)]
+  procs = [ctx.Process(target=_worker, args=(r, world, port, q, chunks, exchange)) for r in range(world)]
   for p in procs:
     p.start()
-  results = [q.get(timeout=300) for _ in range(2)]
+  results = [q.get(timeout=300) for _ in range(world)]
   for p in procs:
     p.join(timeout=120)
     assert p.exitcode == 0

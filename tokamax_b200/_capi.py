@@ -23,6 +23,7 @@ ERR_CUDA = 4
 ERR_WORKSPACE = 5
 ERR_DEVICE_TIMEOUT = 6
 ERR_TOO_LARGE = 7
+ERR_DEVICE_STATE = 8
 
 BF16, F16, F32, F8E4M3, S8 = 0, 1, 2, 3, 4
 RHS_GKN, RHS_GNK = 0, 1
@@ -56,8 +57,12 @@ EXPORTED_SYMBOLS = (
     "tkmx_ragged_gather",
     "tkmx_ragged_scatter",
     "tkmx_ragged_gather_reduce",
-    "tkmx_moe_scatter_rows_p2p",
     "tkmx_moe_sort_pairs_static",
+    "tkmx_moe_sort_pairs_inverse",
+    "tkmx_ep_plan_bytes",
+    "tkmx_ep_exchange_plan",
+    "tkmx_ep_moe_fused",
+    "tkmx_cross_rank_barrier",
 )
 
 
@@ -121,8 +126,17 @@ def load() -> ctypes.CDLL:
     lib.tkmx_ragged_dot_fwd_cyclic.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, ctypes.c_int,
                                                ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                                i64, i64, cfgp, vp, sz, vp]
-    lib.tkmx_moe_scatter_rows_p2p.restype = ctypes.c_int
-    lib.tkmx_moe_scatter_rows_p2p.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp, vp]
+    lib.tkmx_moe_sort_pairs_inverse.restype = ctypes.c_int
+    lib.tkmx_moe_sort_pairs_inverse.argtypes = [vp, i64, i32, vp, vp, vp, vp, sz, vp]
+    lib.tkmx_ep_plan_bytes.restype = sz
+    lib.tkmx_ep_plan_bytes.argtypes = [i32, i32]
+    lib.tkmx_ep_exchange_plan.restype = ctypes.c_int
+    lib.tkmx_ep_exchange_plan.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, ctypes.c_uint32, i64, vp]
+    lib.tkmx_ep_moe_fused.restype = ctypes.c_int
+    lib.tkmx_ep_moe_fused.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i32, i64, i64, i32, i32, i32, i64,
+                                      ctypes.c_int, ctypes.c_int, cfgp, vp]
+    lib.tkmx_cross_rank_barrier.restype = ctypes.c_int
+    lib.tkmx_cross_rank_barrier.argtypes = [vp, vp, i32, i32, ctypes.c_uint32, i64, vp]
     lib.tkmx_moe_sort_workspace_bytes.restype = sz
     lib.tkmx_moe_sort_workspace_bytes.argtypes = [i64, i32]
     lib.tkmx_moe_sort_pairs.restype = ctypes.c_int
@@ -160,7 +174,7 @@ def check(status: int, what: str) -> None:
   lib = load()
   msg = f"{what}: {lib.tkmx_status_string(status).decode()}"
   detail = lib.tkmx_last_cuda_error().decode()
-  if status in (ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_TOO_LARGE) and detail:
+  if status in (ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_TOO_LARGE, ERR_DEVICE_STATE) and detail:
     msg += f" ({detail})"
   if status in (ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_TOO_LARGE):
     raise NotImplementedError(msg)
@@ -285,15 +299,59 @@ def ragged_dot_fwd_cyclic(lhs, rhs, group_sizes, out, *, rhs_scale=None, rhs_lay
   check(st, "tkmx_ragged_dot_fwd_cyclic")
 
 
-def moe_scatter_rows_p2p(src, src_row, dst_peer, dst_row, peer_base, capacity_rows: int, overflow_flag):
-  """Writes rows of `src` into peer-mapped buffers: row i -> peer_base[dst_peer[i]][dst_row[i]].
-  peer_base is an int64 device tensor of base addresses; overflow_flag an int32 device scalar."""
-  dev = _require_cuda(src, src_row, dst_peer, dst_row, peer_base, overflow_flag)
+def moe_sort_pairs_inverse(expert_ids: torch.Tensor, num_experts: int, pos, sorted_pair, counts, workspace):
+  """`moe_sort_pairs` into caller-owned outputs, plus sorted_pair[pos[p]] = p (int32 [num_pairs])."""
+  dev = _require_cuda(expert_ids, pos, sorted_pair, counts, workspace)
+  if expert_ids.dtype != torch.int32:
+    raise ValueError("expert_ids must be int32")
   with torch.cuda.device(dev):
-    st = load().tkmx_moe_scatter_rows_p2p(
-        _ptr(src), _ptr(src_row), _ptr(dst_peer), _ptr(dst_row), _ptr(peer_base), dst_peer.numel(),
-        src.shape[1] * src.element_size(), capacity_rows, _ptr(overflow_flag), _stream(dev))
-  check(st, "tkmx_moe_scatter_rows_p2p")
+    st = load().tkmx_moe_sort_pairs_inverse(
+        _ptr(expert_ids), expert_ids.numel(), num_experts, _ptr(pos), _ptr(sorted_pair), _ptr(counts),
+        _ptr(workspace), workspace.numel() * workspace.element_size(), _stream(dev))
+  check(st, "tkmx_moe_sort_pairs_inverse")
+
+
+def moe_sort_workspace_bytes(num_pairs: int, num_experts: int) -> int:
+  return int(load().tkmx_moe_sort_workspace_bytes(num_pairs, num_experts))
+
+
+EP_MAX_WORLD = 16
+EP_TAB_RECV, EP_TAB_ARRIVE, EP_TAB_RET, EP_TAB_COUNTS, EP_TAB_FLAGS = range(5)
+
+
+def ep_plan_ints(num_experts: int, world: int) -> int:
+  return int(load().tkmx_ep_plan_bytes(num_experts, world)) // 4
+
+
+def ep_exchange_plan(my_counts, peer_table, counts_all, flags, arrive, plan, num_experts: int, world: int,
+                     rank: int, sequence: int, timeout_ns: int) -> None:
+  """Counts all-gather through peer memory + flag barrier + the step's offset tables."""
+  dev = _require_cuda(my_counts, peer_table, counts_all, flags, arrive, plan)
+  with torch.cuda.device(dev):
+    st = load().tkmx_ep_exchange_plan(_ptr(my_counts), _ptr(peer_table), _ptr(counts_all), _ptr(flags),
+                                      _ptr(arrive), _ptr(plan), num_experts, world, rank,
+                                      sequence & 0xFFFFFFFF, timeout_ns, _stream(dev))
+  check(st, "tkmx_ep_exchange_plan")
+
+
+def ep_moe_fused(tokens, sorted_pair, recv, rhs_local, plan, peer_table, arrive, top_k: int, num_experts: int,
+                 world: int, rank: int, n: int, phases: int = 3, config: Config | None = None) -> None:
+  """The fused dispatch + grouped GEMM + return kernel (see include/tokamax_b200.h)."""
+  dev = _require_cuda(tokens, sorted_pair, recv, rhs_local, plan, peer_table, arrive)
+  with torch.cuda.device(dev):
+    st = load().tkmx_ep_moe_fused(_ptr(tokens), _ptr(sorted_pair), _ptr(recv), _ptr(rhs_local), _ptr(plan),
+                                  _ptr(peer_table), _ptr(arrive), tokens.shape[0], top_k, tokens.shape[1], n,
+                                  num_experts, world, rank, recv.shape[0], dtype_code(tokens.dtype), phases,
+                                  _cfg(config), _stream(dev))
+  check(st, "tkmx_ep_moe_fused")
+
+
+def cross_rank_barrier(peer_table, flags, world: int, rank: int, sequence: int, timeout_ns: int) -> None:
+  dev = _require_cuda(peer_table, flags)
+  with torch.cuda.device(dev):
+    st = load().tkmx_cross_rank_barrier(_ptr(peer_table), _ptr(flags), world, rank, sequence & 0xFFFFFFFF,
+                                        timeout_ns, _stream(dev))
+  check(st, "tkmx_cross_rank_barrier")
 
 
 def moe_sort_pairs(expert_ids: torch.Tensor, num_experts: int, workspace: torch.Tensor | None = None):

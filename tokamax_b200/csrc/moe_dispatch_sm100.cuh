@@ -106,10 +106,12 @@ moe_sort_scan_kernel(int32_t* __restrict__ scratch, int num_chunks, int num_expe
   }
 }
 
-// 3. pos[p] = first position of (chunk, expert) + stable rank inside the chunk.
+// 3. pos[p] = first position of (chunk, expert) + stable rank inside the chunk; optionally also
+//    sorted_pair[pos[p]] = p (which pair sits at each sorted position).
 __global__ void __launch_bounds__(kSortChunk)
 moe_sort_scatter_kernel(const int32_t* __restrict__ expert_ids, int num_pairs, int num_experts,
-                        const int32_t* __restrict__ scratch, int32_t* __restrict__ pos) {
+                        const int32_t* __restrict__ scratch, int32_t* __restrict__ pos,
+                        int32_t* __restrict__ sorted_pair) {
   extern __shared__ int warp_hist[];
   const int p = blockIdx.x * kSortChunk + threadIdx.x;
   int e = p < num_pairs ? expert_ids[p] : -1;
@@ -126,9 +128,12 @@ moe_sort_scatter_kernel(const int32_t* __restrict__ expert_ids, int num_pairs, i
     }
   }
   __syncthreads();
-  if (p < num_pairs)
-    pos[p] = e < 0 ? -1
-                   : scratch[blockIdx.x * num_experts + e] + warp_hist[warp * num_experts + e] + rank_in_warp;
+  if (p < num_pairs) {
+    const int at = e < 0 ? -1
+                         : scratch[blockIdx.x * num_experts + e] + warp_hist[warp * num_experts + e] + rank_in_warp;
+    pos[p] = at;
+    if (sorted_pair != nullptr && at >= 0) sorted_pair[at] = p;   // the inverse permutation
+  }
 }
 
 // dst[pos[p], :] = src[p / top_k, :]; one warp per pair, 16-byte pieces.  row_bytes % 16 == 0.
@@ -144,34 +149,6 @@ moe_gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict_
     const uint4* s = src + static_cast<size_t>(p / top_k) * row_vec;
     uint4* o = dst + static_cast<size_t>(d) * row_vec;
     for (int i = lane; i < row_vec; i += 32) o[i] = __ldg(s + i);
-  }
-}
-
-// Row scatter to peer GPUs: row i of `src` (or row src_row[i]) is written to row dst_row[i]
-// of the buffer of rank dst_peer[i], whose base address is peer_base[dst_peer[i]] (a
-// peer-mapped pointer; plain 16-byte stores travel over NVLink, one warp per row so every
-// store instruction covers 512 contiguous bytes).  Rows with dst_peer < 0 or dst_row outside
-// [0, capacity_rows) are skipped; the latter also raise the overflow flag.
-__global__ void __launch_bounds__(256)
-moe_scatter_rows_p2p_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ src_row,
-                            const int32_t* __restrict__ dst_peer, const int32_t* __restrict__ dst_row,
-                            const uint64_t* __restrict__ peer_base, int num_rows, int row_vec,
-                            int capacity_rows, int32_t* __restrict__ overflow_flag) {
-  const int warps_per_block = blockDim.x >> 5;
-  const int lane = threadIdx.x & 31;
-  for (int i = blockIdx.x * warps_per_block + (threadIdx.x >> 5); i < num_rows;
-       i += gridDim.x * warps_per_block) {
-    const int peer = dst_peer[i];
-    if (peer < 0) continue;
-    const int d = dst_row[i];
-    if (d < 0 || d >= capacity_rows) {
-      if (lane == 0) atomicExch(overflow_flag, 1);
-      continue;
-    }
-    const int sr = src_row != nullptr ? src_row[i] : i;
-    const uint4* s = src + static_cast<size_t>(sr) * row_vec;
-    uint4* o = reinterpret_cast<uint4*>(peer_base[peer]) + static_cast<size_t>(d) * row_vec;
-    for (int j = lane; j < row_vec; j += 32) o[j] = __ldg(s + j);
   }
 }
 

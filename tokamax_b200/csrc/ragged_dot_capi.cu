@@ -9,6 +9,8 @@
 #include <cstdlib>
 #include <mutex>
 #include <string>
+#include <utility>
+#include <vector>
 
 #include "../../include/tokamax_b200.h"
 #include "group_info_sm100.cuh"
@@ -40,7 +42,7 @@ __device__ int32_t g_device_status;
 // Tile counters for dynamically scheduled launches: (epoch << 32 | next tile) words, one per
 // launch in flight, handed out round-robin by launch number.  A word is reset by the first
 // CTA of a launch that finds another epoch in it, so nothing is cleaned up afterwards.
-constexpr int kSchedWords = 256;
+constexpr int kSchedWords = 1024;
 __device__ unsigned long long g_sched_words[2 * kSchedWords];   // per launch: {counter, units finished}
 
 constexpr int kMaxDevices = 64;
@@ -149,7 +151,10 @@ void assign_sched(const DeviceInfo& dev, RaggedGemmParams* p, bool default_on) {
   if (env_int("TKMX_DYNAMIC", default_on ? 1 : 0, 0, 1) == 0 || dev.sched_words == nullptr) return;
   uint32_t seq = ++g_launch_seq;
   if (seq == 0) seq = ++g_launch_seq;   // epoch 0 is what a fresh word holds
-  p->sched_slot = dev.sched_words + 2 * (seq % kSchedWords);
+  // TKMX_SCHED_SLOT pins the word (tests: two launches on one word must end with an error
+  // status, not with silently skipped tiles).
+  const int forced = env_int("TKMX_SCHED_SLOT", -1, -1, kSchedWords - 1);
+  p->sched_slot = dev.sched_words + 2 * (forced >= 0 ? uint32_t(forced) : seq % kSchedWords);
   p->sched_epoch = seq;
 }
 
@@ -198,14 +203,40 @@ int resolve_config(const tkmx_config* c, int64_t cols, int num_groups, bool need
   return TKMX_OK;
 }
 
-template <int kMode, int kBlockN, bool kPair>
+// The opt-in shared-memory limit of a kernel is raised once per (device, kernel) to the
+// device maximum, under the mutex: setting it per launch to that launch's size would let two
+// host threads with different ring depths lower it under each other.
+int raise_smem_limit_impl(const void* kernel) {
+  static std::vector<std::pair<const void*, int>> done;   // (kernel, device) pairs already raised
+  int dev = 0;
+  TKMX_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return TKMX_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  for (const auto& d : done)
+    if (d.first == kernel && d.second == dev) return TKMX_OK;
+  const int cap = g_devices[dev].smem_optin > 0 && g_devices[dev].smem_optin < kMaxSmemOptin
+                      ? g_devices[dev].smem_optin : kMaxSmemOptin;
+  TKMX_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
+  done.emplace_back(kernel, dev);
+  return TKMX_OK;
+}
+template <typename Kernel>
+int raise_smem_limit(Kernel kernel, int /*smem_needed*/) {
+  return raise_smem_limit_impl(reinterpret_cast<const void*>(kernel));
+}
+
+template <int kMode, int kBlockN, bool kPair, bool kEp = false>
 int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
-               const RaggedGemmParams& p, int grid, cudaStream_t stream) {
-  auto kernel = tkmx::ragged_gemm_kernel<kMode, kBlockN, kPair>;
+               const RaggedGemmParams& p, int grid, cudaStream_t stream,
+               const tkmx::EpFusedParams& ep = tkmx::EpFusedParams{}) {
+  auto kernel = tkmx::ragged_gemm_kernel<kMode, kBlockN, kPair, kEp>;
   const bool need_ts = kMode != tkmx::kContract;
   const int smem =
-      tkmx::make_smem_layout(kBlockN, kPair, p.num_stages, p.num_groups, need_ts).total + 1024;
-  TKMX_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      tkmx::make_smem_layout(kBlockN, kPair, p.num_stages, p.num_groups, need_ts, kEp ? ep.num_experts : 0).total + 1024;
+  {
+    const int st = raise_smem_limit(kernel, smem);
+    if (st != TKMX_OK) return st;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(tkmx::kNumThreads, 1, 1);
@@ -218,7 +249,28 @@ int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  TKMX_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, p));
+  if constexpr (kEp) {
+    // In the expert-parallel form CTAs wait for rows that other CTAs of the same grid send, so
+    // the whole grid has to be resident at once: never launch more CTAs than fit together.
+    int fit = 0;
+    if constexpr (kPair) {
+      int clusters = 0;
+      TKMX_CUDA_OK(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+      fit = clusters * 2;
+    } else {
+      int per_sm = 0, dev = 0, sms = 0;
+      TKMX_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, tkmx::kNumThreads, smem));
+      TKMX_CUDA_OK(cudaGetDevice(&dev));
+      TKMX_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      fit = per_sm * sms;
+    }
+    if (fit < (kPair ? 2 : 1)) {
+      g_last_cuda_error = "the expert-parallel kernel does not fit on this device";
+      return TKMX_ERR_CUDA;
+    }
+    if (grid > fit) cfg.gridDim = dim3(fit, 1, 1);
+  }
+  TKMX_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, p, ep));
   return TKMX_OK;
 }
 
@@ -395,7 +447,10 @@ int launch_w8(const CUtensorMap& ma, const CUtensorMap& mb, const RaggedGemmPara
               cudaStream_t stream) {
   auto kernel = tkmx::ragged_gemm_w8_kernel<kBlockN, kPair, kQuant>;
   const int smem = tkmx::make_w8_smem_layout(kBlockN, kPair, p.num_stages, p.num_groups).total + 1024;
-  TKMX_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  {
+    const int st = raise_smem_limit(kernel, smem);
+    if (st != TKMX_OK) return st;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(tkmx::kW8Threads, 1, 1);
@@ -417,7 +472,10 @@ int launch_f8(const CUtensorMap& ma, const CUtensorMap& ma32, const CUtensorMap&
               const RaggedGemmParams& p, const float* row_scale, int grid, cudaStream_t stream) {
   auto kernel = tkmx::ragged_gemm_f8_kernel<kBlockN, kPair>;
   const int smem = tkmx::make_f8_smem_layout(kBlockN, kPair, p.num_stages, p.num_groups).total + 1024;
-  TKMX_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  {
+    const int st = raise_smem_limit(kernel, smem);
+    if (st != TKMX_OK) return st;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(tkmx::kF8Threads, 1, 1);
@@ -634,6 +692,7 @@ const char* tkmx_status_string(int status) {
     case TKMX_ERR_WORKSPACE: return "workspace too small";
     case TKMX_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
     case TKMX_ERR_TOO_LARGE: return "size beyond a static limit";
+    case TKMX_ERR_DEVICE_STATE: return "a kernel found its bookkeeping inconsistent and stopped early";
   }
   return "unknown status";
 }
@@ -842,16 +901,18 @@ size_t tkmx_moe_sort_workspace_bytes(int64_t num_pairs, int32_t num_experts) {
 }
 
 static int moe_sort_launch(const int32_t* expert_ids, int64_t num_pairs, int32_t num_experts,
-                           int32_t* pos, int32_t* expert_counts, int32_t* scratch, cudaStream_t stream) {
+                           int32_t* pos, int32_t* expert_counts, int32_t* scratch, cudaStream_t stream,
+                           int32_t* sorted_pair = nullptr) {
   const int chunks = int((num_pairs + tkmx::kSortChunk - 1) / tkmx::kSortChunk);
   const int smem = 32 * num_experts * int(sizeof(int));
   if (smem > 48 * 1024) {
-    TKMX_CUDA_OK(cudaFuncSetAttribute(tkmx::moe_sort_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    TKMX_CUDA_OK(cudaFuncSetAttribute(tkmx::moe_sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    int st = raise_smem_limit(tkmx::moe_sort_hist_kernel, smem);
+    if (st == TKMX_OK) st = raise_smem_limit(tkmx::moe_sort_scatter_kernel, smem);
+    if (st != TKMX_OK) return st;
   }
   tkmx::moe_sort_hist_kernel<<<chunks, tkmx::kSortChunk, smem, stream>>>(expert_ids, int(num_pairs), num_experts, scratch);
   tkmx::moe_sort_scan_kernel<<<1, 1024, 0, stream>>>(scratch, chunks, num_experts, expert_counts);
-  tkmx::moe_sort_scatter_kernel<<<chunks, tkmx::kSortChunk, smem, stream>>>(expert_ids, int(num_pairs), num_experts, scratch, pos);
+  tkmx::moe_sort_scatter_kernel<<<chunks, tkmx::kSortChunk, smem, stream>>>(expert_ids, int(num_pairs), num_experts, scratch, pos, sorted_pair);
   TKMX_CUDA_OK(cudaGetLastError());
   return TKMX_OK;
 }
@@ -859,6 +920,13 @@ static int moe_sort_launch(const int32_t* expert_ids, int64_t num_pairs, int32_t
 int tkmx_moe_sort_pairs(const int32_t* expert_ids, int64_t num_pairs, int32_t num_experts, int32_t* pos,
                         int32_t* expert_counts, void* workspace, size_t workspace_bytes,
                         void* cuda_stream) {
+  return tkmx_moe_sort_pairs_inverse(expert_ids, num_pairs, num_experts, pos, nullptr, expert_counts, workspace,
+                                     workspace_bytes, cuda_stream);
+}
+
+int tkmx_moe_sort_pairs_inverse(const int32_t* expert_ids, int64_t num_pairs, int32_t num_experts, int32_t* pos,
+                                int32_t* sorted_pair, int32_t* expert_counts, void* workspace,
+                                size_t workspace_bytes, void* cuda_stream) {
   if (num_pairs < 0 || num_experts <= 0) return TKMX_ERR_INVALID_ARGUMENT;
   if (num_experts > tkmx::kSortMaxExperts || !fits_i32(num_pairs)) return TKMX_ERR_TOO_LARGE;
   if (expert_counts == nullptr) return TKMX_ERR_INVALID_ARGUMENT;
@@ -873,7 +941,7 @@ int tkmx_moe_sort_pairs(const int32_t* expert_ids, int64_t num_pairs, int32_t nu
   int st = get_device_info(&dev);
   if (st != TKMX_OK) return st;
   return moe_sort_launch(expert_ids, num_pairs, num_experts, pos, expert_counts,
-                         static_cast<int32_t*>(workspace), stream);
+                         static_cast<int32_t*>(workspace), stream, sorted_pair);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -934,27 +1002,6 @@ int tkmx_moe_gather_rows(const void* src, const int32_t* pos, void* dst, int64_t
   const int grid = dev->num_sms * 8;
   tkmx::moe_gather_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
       static_cast<const uint4*>(src), pos, static_cast<uint4*>(dst), int(num_pairs), top_k, int(row_bytes / 16));
-  TKMX_CUDA_OK(cudaGetLastError());
-  return TKMX_OK;
-}
-
-int tkmx_moe_scatter_rows_p2p(const void* src, const int32_t* src_row, const int32_t* dst_peer,
-                              const int32_t* dst_row, const uint64_t* peer_base, int64_t num_rows,
-                              int64_t row_bytes, int64_t capacity_rows, int32_t* overflow_flag,
-                              void* cuda_stream) {
-  if (num_rows < 0 || row_bytes < 0 || capacity_rows < 0) return TKMX_ERR_INVALID_ARGUMENT;
-  if (num_rows == 0 || row_bytes == 0) return TKMX_OK;
-  if (src == nullptr || dst_peer == nullptr || dst_row == nullptr || peer_base == nullptr ||
-      overflow_flag == nullptr)
-    return TKMX_ERR_INVALID_ARGUMENT;
-  if (row_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(src) & 15u)) return TKMX_ERR_ALIGNMENT;
-  if (!fits_i32(num_rows) || !fits_i32(row_bytes / 16) || !fits_i32(capacity_rows)) return TKMX_ERR_TOO_LARGE;
-  DeviceInfo* dev = nullptr;
-  int st = get_device_info(&dev);
-  if (st != TKMX_OK) return st;
-  tkmx::moe_scatter_rows_p2p_kernel<<<dev->num_sms * 8, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
-      static_cast<const uint4*>(src), src_row, dst_peer, dst_row, peer_base, int(num_rows),
-      int(row_bytes / 16), int(capacity_rows), overflow_flag);
   TKMX_CUDA_OK(cudaGetLastError());
   return TKMX_OK;
 }
@@ -1035,6 +1082,164 @@ int tkmx_ragged_gather_reduce(const void* x, const int32_t* indices, const float
   return TKMX_OK;
 }
 
+// ---------------------------------------------------------------------------------------
+// Expert-parallel layer over peer-mapped memory.
+size_t tkmx_ep_plan_bytes(int32_t num_experts, int32_t world) {
+  if (num_experts <= 0 || world <= 0 || num_experts % world != 0) return 0;
+  return size_t(tkmx::ep_plan_layout(num_experts, world).total) * sizeof(int32_t);
+}
+
+static int ep_check_world(int32_t num_experts, int32_t world, int32_t rank) {
+  if (num_experts <= 0 || world <= 0 || rank < 0 || rank >= world || num_experts % world != 0)
+    return TKMX_ERR_INVALID_ARGUMENT;
+  if (world > tkmx::kEpMaxWorld || num_experts > 1024) return TKMX_ERR_TOO_LARGE;
+  return TKMX_OK;
+}
+
+int tkmx_cross_rank_barrier(const uint64_t* peer_table, uint32_t* flags_local, int32_t world, int32_t rank,
+                            uint32_t sequence, int64_t timeout_ns, void* cuda_stream) {
+  if (peer_table == nullptr || flags_local == nullptr || world <= 0 || rank < 0 || rank >= world || timeout_ns <= 0)
+    return TKMX_ERR_INVALID_ARGUMENT;
+  if (world > tkmx::kEpMaxWorld) return TKMX_ERR_TOO_LARGE;
+  DeviceInfo* dev = nullptr;
+  int st = get_device_info(&dev);
+  if (st != TKMX_OK) return st;
+  tkmx::cross_rank_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      peer_table, flags_local, world, rank, sequence, uint64_t(timeout_ns), dev->status_ptr);
+  TKMX_CUDA_OK(cudaGetLastError());
+  return TKMX_OK;
+}
+
+int tkmx_ep_exchange_plan(const int32_t* my_counts, const uint64_t* peer_table, int32_t* counts_all_local,
+                          uint32_t* flags_local, uint32_t* arrive_local, int32_t* plan, int32_t num_experts,
+                          int32_t world, int32_t rank, uint32_t sequence, int64_t timeout_ns, void* cuda_stream) {
+  int st = ep_check_world(num_experts, world, rank);
+  if (st != TKMX_OK) return st;
+  if (my_counts == nullptr || peer_table == nullptr || counts_all_local == nullptr || flags_local == nullptr ||
+      arrive_local == nullptr || plan == nullptr || timeout_ns <= 0)
+    return TKMX_ERR_INVALID_ARGUMENT;
+  DeviceInfo* dev = nullptr;
+  st = get_device_info(&dev);
+  if (st != TKMX_OK) return st;
+  tkmx::EpExchangeParams x = {};
+  x.my_counts = my_counts;
+  x.peer_tab = peer_table;
+  x.counts_all = counts_all_local;
+  x.flags = flags_local;
+  x.arrive = arrive_local;
+  x.plan = plan;
+  x.num_experts = num_experts;
+  x.world = world;
+  x.rank = rank;
+  x.seq = sequence;
+  x.timeout_ns = uint64_t(timeout_ns);
+  x.status = dev->status_ptr;
+  tkmx::ep_exchange_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(cuda_stream)>>>(x);
+  TKMX_CUDA_OK(cudaGetLastError());
+  return TKMX_OK;
+}
+
+int tkmx_ep_moe_fused(const void* tokens, const int32_t* sorted_pair, const void* recv_local,
+                      const void* rhs_local, const int32_t* plan, const uint64_t* peer_table,
+                      const uint32_t* arrive_local, int64_t num_tokens, int32_t top_k, int64_t k, int64_t n,
+                      int32_t num_experts, int32_t world, int32_t rank, int64_t capacity_rows, int dtype,
+                      int phases, const tkmx_config* config, void* cuda_stream) {
+  int st = ep_check_world(num_experts, world, rank);
+  if (st != TKMX_OK) return st;
+  if (num_tokens < 0 || top_k <= 0 || k <= 0 || n <= 0 || capacity_rows <= 0 || phases < 1 || phases > 3)
+    return TKMX_ERR_INVALID_ARGUMENT;
+  if (dtype != TKMX_BF16 && dtype != TKMX_F16) return TKMX_ERR_UNSUPPORTED;
+  if (k % 8 != 0 || n % 8 != 0) return TKMX_ERR_ALIGNMENT;   // rows move and return in 16-byte pieces
+  if (!fits_i32(num_tokens * top_k) || !fits_i32(k) || !fits_i32(n) || !fits_i32(capacity_rows) ||
+      !fits_i32(capacity_rows + 256 * int64_t(num_experts / world + 1)) || !fits_i32(n * 2))
+    return TKMX_ERR_TOO_LARGE;
+  if (num_tokens == 0) return TKMX_OK;
+  if (tokens == nullptr || sorted_pair == nullptr || recv_local == nullptr || rhs_local == nullptr ||
+      plan == nullptr || peer_table == nullptr || arrive_local == nullptr)
+    return TKMX_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(tokens) & 15u) != 0) return TKMX_ERR_ALIGNMENT;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  const int gl = num_experts / world;
+
+  DeviceInfo* dev = nullptr;
+  st = get_device_info(&dev);
+  if (st != TKMX_OK) return st;
+  ResolvedConfig rc;
+  tkmx_config c = {};
+  if (config != nullptr) c = *config;
+  c.block_n = 256;   // the only width built for this form
+  st = resolve_config(&c, n, gl, true, *dev, &rc);
+  if (st != TKMX_OK) return st;
+  // the ring may have to give room to the send-order table
+  while (rc.num_stages > 2 &&
+         tkmx::make_smem_layout(rc.block_n, rc.pair, rc.num_stages, gl, true, num_experts).total + 1024 >
+             uint32_t(dev->smem_optin < kMaxSmemOptin ? dev->smem_optin : kMaxSmemOptin))
+    --rc.num_stages;
+
+  CUtensorMap ma, mb, mo = {};
+  {
+    const uint64_t dims[2] = {uint64_t(k), uint64_t(capacity_rows)};
+    const uint64_t strides[1] = {uint64_t(k) * 2};
+    const uint32_t box[2] = {64, 128};
+    st = encode_map(&ma, recv_local, 2, dims, strides, box);
+    if (st != TKMX_OK) return st;
+  }
+  {
+    const uint64_t dims[3] = {uint64_t(n), uint64_t(k), uint64_t(gl)};
+    const uint64_t strides[2] = {uint64_t(n) * 2, uint64_t(n) * uint64_t(k) * 2};
+    const uint32_t box[3] = {64, 64, 1};
+    st = encode_map(&mb, rhs_local, 3, dims, strides, box);
+    if (st != TKMX_OK) return st;
+  }
+  const tkmx::EpPlanLayout pl = tkmx::ep_plan_layout(num_experts, world);
+  RaggedGemmParams p = {};
+  p.group_sizes = plan + pl.group_sizes;
+  p.out = nullptr;
+  p.m_total = int32_t(capacity_rows);
+  p.rows = int32_t(capacity_rows);
+  p.cols = int32_t(n);
+  p.cdim = int32_t(k);
+  p.num_groups = gl;
+  p.rhs_groups = gl;
+  p.group_begin = 0;
+  p.group_end = gl;
+  p.skip_zero_fill = 1;
+  p.out_is_f32 = 0;
+  p.out_is_f16 = dtype == TKMX_F16;
+  p.out_vec_ok = 1;
+  const uint32_t fmt = dtype == TKMX_BF16 ? 1u : 0u;
+  p.idesc = tkmx::ptx::make_idesc(fmt, fmt, 0u, 1u, rc.pair ? 256u : 128u, uint32_t(rc.block_n));
+  p.tile_width = rc.tile_width;
+  p.minor_is_m = rc.minor_is_m;
+  p.num_stages = rc.num_stages;
+  p.status = dev->status_ptr;
+  p.tma_store = 0;
+  assign_sched(*dev, &p, true);
+  p.swap_rows = rc.pair ? env_int("TKMX_SWAP_ROWS", 192, 0, 192) : 0;
+
+  tkmx::EpFusedParams ep = {};
+  ep.tokens = tokens;
+  ep.sorted_pair = sorted_pair;
+  ep.plan = plan;
+  ep.peer_tab = peer_table;
+  ep.arrive = arrive_local;
+  ep.world = world;
+  ep.rank = rank;
+  ep.top_k = top_k;
+  ep.num_experts = num_experts;
+  ep.row_vec = int32_t(k * 2 / 16);
+  ep.ret_row_bytes = int32_t(n * 2);
+  ep.capacity_rows = int32_t(capacity_rows);
+  ep.phases = phases;
+
+  // Every SM takes part (its two sender warps do, even when it draws no tile).
+  int grid = dev->num_sms;
+  if (rc.max_ctas > 0 && rc.max_ctas < grid) grid = rc.max_ctas;
+  if (rc.pair) grid = std::max(2, grid / 2 * 2);
+  if (rc.pair) return launch_one<tkmx::kRowsBN, 256, true, true>(ma, mb, mo, p, grid, stream, ep);
+  return launch_one<tkmx::kRowsBN, 256, false, true>(ma, mb, mo, p, grid, stream, ep);
+}
+
 int tkmx_device_status(void) {
   DeviceInfo* dev = nullptr;
   int st = get_device_info(&dev);
@@ -1045,7 +1250,14 @@ int tkmx_device_status(void) {
   if (v != 0) {
     TKMX_CUDA_OK(cudaMemset(dev->status_ptr, 0, sizeof(v)));
     g_last_cuda_error = "device status word = " + std::to_string(v);
-    return TKMX_ERR_DEVICE_TIMEOUT;
+    if (v == tkmx::kDevSchedConflict)
+      g_last_cuda_error += " (two launches in flight shared one tile-counter word: more than " +
+                           std::to_string(kSchedWords) + " dynamically scheduled launches overlapped, or a replayed "
+                           "graph ran beside eager launches; results of both are incomplete)";
+    if (v == tkmx::kDevEpOverflow)
+      g_last_cuda_error += " (expert-parallel rows aimed outside a receive buffer were dropped)";
+    return (v == tkmx::kDevSchedConflict || v == tkmx::kDevEpOverflow) ? TKMX_ERR_DEVICE_STATE
+                                                                      : TKMX_ERR_DEVICE_TIMEOUT;
   }
   return TKMX_OK;
 }

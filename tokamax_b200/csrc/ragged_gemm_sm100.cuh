@@ -53,6 +53,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "ep_fused_sm100.cuh"
 #include "ptx_sm100.cuh"
 
 namespace tkmx {
@@ -66,6 +67,8 @@ enum DeviceStatus : int {
   kDevTimeoutMma = 2,
   kDevTimeoutEpilogue = 3,
   kDevTimeoutFixup = 4,
+  // 5-7: expert-parallel waits and overflow (ep_fused_sm100.cuh)
+  kDevSchedConflict = 8,   // another launch took this launch's tile-counter word while it was drawing
 };
 
 struct RaggedGemmParams {
@@ -127,11 +130,13 @@ struct SmemLayout {
   uint32_t abort_flag;  // int
   uint32_t row_start;   // int32[G + 1]
   uint32_t tile_start;  // int32[G + 1]  (rows modes only)
+  uint32_t ep_vstart;   // int32[ep_experts + 1]: send-order prefix sums of the expert-parallel form
   uint32_t total;
 };
 
 __host__ __device__ inline SmemLayout make_smem_layout(int block_n, bool pair, int num_stages,
-                                                       int num_groups, bool need_tile_start) {
+                                                       int num_groups, bool need_tile_start,
+                                                       int ep_experts = 0) {
   SmemLayout l;
   l.ring = 0;
   uint32_t off = static_cast<uint32_t>(num_stages) * stage_bytes(block_n, pair);
@@ -150,6 +155,8 @@ __host__ __device__ inline SmemLayout make_smem_layout(int block_n, bool pair, i
   off += 4u * (num_groups + 1);
   l.tile_start = off;
   if (need_tile_start) off += 4u * (num_groups + 1);
+  l.ep_vstart = off;
+  if (ep_experts > 0) off += 4u * (ep_experts + 1);
   l.total = off;
   return l;
 }
@@ -200,8 +207,12 @@ __device__ __forceinline__ void claim_word(unsigned long long* word, uint32_t ep
     old = seen;
   }
 }
-__device__ __forceinline__ int draw_tile(unsigned long long* word) {
-  return static_cast<int>(atomicAdd(word, 1ull) & 0xFFFFFFFFull);
+// Returns the whole (epoch << 32 | tile) word: the caller checks that the epoch is still its
+// own.  Another epoch means a second launch was given the same word while this one was still
+// drawing (more launches in flight than there are words, or a replayed graph beside eager
+// launches); the tile numbers handed out since then cannot be trusted by either launch.
+__device__ __forceinline__ unsigned long long draw_tile(unsigned long long* word) {
+  return atomicAdd(word, 1ull);
 }
 // Called by a unit once it has drawn its end-of-work mark (it never draws again).  The last
 // unit puts the count back to zero under the same epoch, so that a launch repeated with
@@ -272,21 +283,25 @@ __device__ __forceinline__ int visit_to_group(int v, int cycles, int rhs_groups)
 template <int kTileM, bool kTiles>
 __device__ __forceinline__ void scan_groups(const RaggedGemmParams& p, int* row_start, int* tile_start,
                                             int lane) {
-  int carry_rows = 0;
+  // Cumulative rows saturate at the matrix height, so that a bad group_sizes can neither index
+  // past the matrix nor overflow: every term is <= m_total < 2^31 and sums are formed in
+  // unsigned 32-bit arithmetic before they are clamped again.
+  const uint32_t cap = static_cast<uint32_t>(p.m_total);
+  uint32_t carry_rows = 0;
   for (int g0 = 0; g0 < p.num_groups; g0 += 32) {
     const int g = g0 + lane;
-    const int sz = (g < p.num_groups) ? max(p.group_sizes[g], 0) : 0;
-    int incl = sz;
+    const uint32_t sz = (g < p.num_groups) ? min(static_cast<uint32_t>(max(p.group_sizes[g], 0)), cap) : 0u;
+    uint32_t incl = sz;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += v;
+      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl = min(incl + v, cap);
     }
-    // Clamp cumulative rows to the matrix so a bad group_sizes cannot index past it.
-    if (g < p.num_groups) row_start[g] = min(carry_rows + incl - sz, p.m_total);
-    carry_rows += __shfl_sync(0xffffffffu, incl, 31);
+    const uint32_t before = __shfl_up_sync(0xffffffffu, incl, 1);
+    if (g < p.num_groups) row_start[g] = static_cast<int>(min(carry_rows + (lane == 0 ? 0u : before), cap));
+    carry_rows = min(carry_rows + __shfl_sync(0xffffffffu, incl, 31), cap);
   }
-  if (lane == 0) row_start[p.num_groups] = min(carry_rows, p.m_total);
+  if (lane == 0) row_start[p.num_groups] = static_cast<int>(carry_rows);
   __syncwarp();
   if constexpr (kTiles) {
     const int cycles = visit_cycles(p.num_groups, p.rhs_groups);
@@ -522,11 +537,17 @@ __device__ __forceinline__ void store_chunk(const RaggedGemmParams& p, uint32_t 
   }
 }
 
-template <int kMode, int kBlockN, bool kPair>
+// kEp: the expert-parallel form (rows mode, rhs [G, K, N]).  A is this rank's receive buffer;
+// warps 2 and 3 push this rank's token rows into the owners' receive buffers while the other
+// warps multiply what has arrived (the producer waits on per-expert arrival counters), and the
+// epilogue stores finished rows straight into the source ranks' return buffers (`p.out` unused).
+template <int kMode, int kBlockN, bool kPair, bool kEp = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                   const __grid_constant__ CUtensorMap map_out, const RaggedGemmParams p) {
+                   const __grid_constant__ CUtensorMap map_out, const RaggedGemmParams p,
+                   const __grid_constant__ EpFusedParams ep) {
   static_assert(kBlockN == 64 || kBlockN == 128 || kBlockN == 256, "unsupported BLOCK_N");
+  static_assert(!kEp || kMode == kRowsBN, "the expert-parallel form is a forward over [G, K, N] weights");
   static_assert(!kPair || kBlockN >= 128, "pair mode splits B into two halves of >= 64 columns");
   constexpr int kCtas = kPair ? 2 : 1;
   constexpr int kTileM = kBlockM * kCtas;            // rows of one tile (whole pair)
@@ -556,7 +577,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   uint8_t* base_ptr = smem_raw + (base - raw_addr);
 
   const int num_stages = p.num_stages;
-  const SmemLayout L = make_smem_layout(kBlockN, kPair, num_stages, p.num_groups, kMode != kContract);
+  const SmemLayout L = make_smem_layout(kBlockN, kPair, num_stages, p.num_groups, kMode != kContract,
+                                        kEp ? ep.num_experts : 0);
   const uint32_t bar_full = base + L.bars;
   const uint32_t bar_empty = bar_full + 8u * num_stages;
   const uint32_t bar_tail = bar_empty + 8u * num_stages;
@@ -568,6 +590,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   volatile unsigned long long* tile_q = reinterpret_cast<volatile unsigned long long*>(base_ptr + L.queue);
   int* row_start = reinterpret_cast<int*>(base_ptr + L.row_start);
   int* tile_start = reinterpret_cast<int*>(base_ptr + L.tile_start);
+  int* ep_vstart = reinterpret_cast<int*>(base_ptr + L.ep_vstart);
+  const bool ep_multiply = !kEp || (ep.phases & 2) != 0;   // false: this launch only sends rows
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -658,6 +682,10 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     ptx::tmem_relinquish<kCtas>();
   }
   if (warp == 3) scan_groups<kTileM, kMode != kContract>(p, row_start, tile_start, lane);
+  if constexpr (kEp) {
+    const EpPlanLayout pl = ep_plan_layout(ep.num_experts, ep.world);
+    for (int i = threadIdx.x; i <= ep.num_experts; i += kNumThreads) ep_vstart[i] = __ldg(ep.plan + pl.vstart + i);
+  }
   ptx::tcgen05_fence_before();
   __syncthreads();
   if constexpr (kPair) {
@@ -670,8 +698,9 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
   // ------------------------------------------------------------------ roles
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0 && ep_multiply) {
       // ===== TMA producer (runs in both CTAs of a pair, each for its own operands) =====
+      int ep_ready_group = -1;   // kEp: last local expert whose rows were seen complete
       Walker walk(p, row_start, tile_start, unit, num_units);
       Tile t;
       uint32_t cnt = 0;  // ring slots filled so far
@@ -679,7 +708,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       RingPos pub;               // leader: next queue slot to publish into
       int ahead = 0;             // leader: tiles published but not yet started by this producer
       uint32_t pub_seq = 0;      // leader: tiles published so far
-      int pending = 0;           // leader: tile number drawn ahead, not yet published
+      unsigned long long pending = 0;   // leader: (epoch << 32 | tile number) drawn ahead, not yet published
       bool claimed = false;      // leader: the counter word carries this launch's epoch
       uint32_t seq = 0;          // peer: tiles taken so far
       bool drained = false;      // leader: the end-of-work mark has been published
@@ -703,8 +732,12 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             }
             // `pending` was drawn one publication ago: its atomic has had a whole tile's worth
             // of loads to come back.  The next draw is issued now and looked at next time.
-            int lin = pending;
-            if (lin >= walk.total_tiles) {
+            int lin = static_cast<int>(static_cast<uint32_t>(pending));
+            if (static_cast<uint32_t>(pending >> 32) != p.sched_epoch) {
+              // The word was taken over: stop this unit as at the end of work and report it.
+              atomicCAS(p.status, 0, kDevSchedConflict);
+              lin = -1;
+            } else if (lin >= walk.total_tiles) {
               lin = -1;   // end of work
               finish_drawing(p.sched_slot, p.sched_epoch, num_units);
             } else {
@@ -749,6 +782,18 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int gateup_jump = (kMode == kRowsBN && p.gateup && kLocalN == kBlockN)
                                     ? p.cols / 2 - kBlockN / 2 : 0;  // extra offset of the up chunks
         const int slab = (kMode != kContract && t.group >= 0) ? t.group % p.rhs_groups : 0;
+        if constexpr (kEp) {
+          // The tile's rows come from every rank: wait until the expert's arrival counter has
+          // reached its row count (tiles are visited in expert order, as the rows are sent).
+          if (t.group >= 0 && t.group != ep_ready_group) {
+            const uint32_t expected = static_cast<uint32_t>(row_start[t.group + 1] - row_start[t.group]);
+            if (!ep_wait_expert(ep, t.group, expected, abort_flag, p.status, kWaitBudgetNs)) {
+              ok = false;
+              break;
+            }
+            ep_ready_group = t.group;
+          }
+        }
         for (int kb = 0; kb < t.num_kb; ++kb, ++cnt, pos.advance(num_stages)) {
           const uint32_t s = pos.slot;
           const uint32_t ph = pos.phase;
@@ -841,7 +886,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && cta_rank == 0) {
+    if (lane == 0 && cta_rank == 0 && ep_multiply) {
       // ===== UMMA issuer (the leader CTA issues for the pair) =====
       Walker walk(p, row_start, tile_start, unit, num_units);
       Tile t;
@@ -906,8 +951,14 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
       }
     }
-  } else if (warp == 2) {
-    if constexpr (kMode == kContract) {
+  } else if (warp == 2 || warp == 3) {
+    if constexpr (kEp) {
+      // ===== expert-parallel senders: two warps per CTA, all CTAs of the grid =====
+      if (ep.phases & 1)
+        ep_send_rows(ep, ep_vstart, static_cast<int>(blockIdx.x) * 2 + (warp - 2), static_cast<int>(gridDim.x) * 2,
+                     lane, p.status);
+    }
+    if (kMode == kContract && warp == 2) {
       // ===== tail fix-up: zero the rows of the last contraction block that lie past
       // the end of the group, in both operands, before the MMA may read the slot =====
       Walker walk(p, row_start, tile_start, unit, num_units);
@@ -969,7 +1020,9 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int ld_out = gateup ? p.cols / 2 : p.cols;
     RingPos qpos;
     uint32_t seq = 0;
-    while (ok) {
+    EpRoute route;             // kEp: where the rows of the current expert return to
+    int route_group = -1;
+    while (ok && ep_multiply) {
       {
         const int r = next_tile(walk, t, qpos, seq, kDevTimeoutEpilogue, true);
         if (r <= 0) {
@@ -979,6 +1032,12 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
       const int row = t.row0 + static_cast<int>(cta_rank) * kBlockM + ew * 32 + lane;
       const bool row_ok = row < t.row_end;
+      if constexpr (kEp) {
+        if (t.group >= 0 && t.group != route_group) {
+          route.load(ep, t.group, lane);
+          route_group = t.group;
+        }
+      }
       size_t out_row_off;
       if constexpr (kMode == kContract)
         out_row_off = (static_cast<size_t>(t.group) * p.rows + row) * ld_out;
@@ -1023,6 +1082,22 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         for (int rc = 0; rc * 32 < valid; ++rc) {
           ptx::tmem_ld_32x32b_x32(tmem_row + rc * 32, v);
           ptx::tmem_wait_ld();
+          if constexpr (kEp) {
+            // Lane j works out where tile row rc * 32 + j returns to; per row the warp then
+            // writes its 32 consecutive 16-bit outputs there.
+            const uint64_t my_addr = route.row_address(ep, t.row0 + rc * 32 + lane);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const uint64_t a = shfl64(my_addr, i);
+              if (rc * 32 + i < valid && n_ok) {
+                const float val = __uint_as_float(v[i]);
+                uint16_t* dst = reinterpret_cast<uint16_t*>(a) + n;
+                if (p.out_is_f16) *reinterpret_cast<__half*>(dst) = __float2half_rn(val);
+                else *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16_rn(val);
+              }
+            }
+            continue;
+          }
           const size_t off0 = static_cast<size_t>(t.row0 + rc * 32) * ld_out + n;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -1089,6 +1164,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       const int warp_row0 = t.row0 + static_cast<int>(cta_rank) * kBlockM + ew * 32;
       const bool block_full = (kMode == kContract) ? (warp_row0 < t.row_end) : (warp_row0 + 32 <= t.row_end);
       const bool use_tma = p.tma_store != 0 && block_full;
+      uint64_t ep_row_addr = 0;   // kEp: return address of this lane's row
+      if constexpr (kEp) ep_row_addr = route.row_address(ep, row);
       uint32_t va[32], vb[32];
       if (has_acc) {
         ptx::tmem_ld_32x32b_x32(tmem_row, va);
@@ -1101,6 +1178,40 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       for (int c = 0; c < n_chunks; ++c) {
         const int col = t.col0 + c * 64;
         if (has_acc) ptx::tmem_wait_ld();
+        if constexpr (kEp) {
+          // 32 rows x 64 columns through the swizzled staging block, then out by rows: eight
+          // lanes write one row's 128 contiguous bytes into its source rank's return buffer.
+          uint32_t w[32];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            w[i] = p.out_is_f16 ? pack_f16x2(__uint_as_float(va[2 * i]), __uint_as_float(va[2 * i + 1]))
+                                : pack_bf16x2(__uint_as_float(va[2 * i]), __uint_as_float(va[2 * i + 1]));
+            w[16 + i] = p.out_is_f16 ? pack_f16x2(__uint_as_float(vb[2 * i]), __uint_as_float(vb[2 * i + 1]))
+                                     : pack_bf16x2(__uint_as_float(vb[2 * i]), __uint_as_float(vb[2 * i + 1]));
+          }
+          if (has_acc && c + 1 < n_chunks) {
+            ptx::tmem_ld_32x32b_x32(tmem_row + (c + 1) * 64, va);
+            ptx::tmem_ld_32x32b_x32(tmem_row + (c + 1) * 64 + 32, vb);
+          }
+          uint8_t* block = base_ptr + L.staging + ew * kStagingBytes;
+          __syncwarp();   // the previous chunk's row reads are done
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(block + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          __syncwarp();
+          const int piece = lane & 7;
+          const bool col_ok = col + piece * 8 < p.cols;   // cols is a multiple of 8 in this form
+#pragma unroll
+          for (int rr = 0; rr < 8; ++rr) {
+            const int rl = rr * 4 + (lane >> 3);
+            const uint64_t a = shfl64(ep_row_addr, rl);
+            const bool r_ok = __shfl_sync(0xffffffffu, row_ok ? 1 : 0, rl) != 0;
+            const uint4 val = *reinterpret_cast<const uint4*>(block + rl * 128 + ((piece ^ (rl & 7)) << 4));
+            if (r_ok && col_ok) *reinterpret_cast<uint4*>(a + static_cast<uint64_t>(col + piece * 8) * 2) = val;
+          }
+          continue;
+        }
         if (use_tma) {
           uint32_t w[32];
 #pragma unroll

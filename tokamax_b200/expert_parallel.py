@@ -20,13 +20,16 @@ Per call on every rank:
 The split sizes of the row exchanges are host integers (all_to_all_single wants lists), so
 step 2 ends with one device-to-host read per call.
 
-With `exchange="p2p"` (the default on more than one GPU) steps 3-4 and 6 use no collective
-library on the row path: every rank holds a receive buffer and a return buffer in
-peer-mapped ("symmetric") memory, the per-segment offsets are exchanged on the device, and a
-scatter kernel writes each token row straight into the owning rank's receive buffer -- and
-each output row straight back into the source rank's return buffer -- with plain stores
-over NVLink, bracketed by stream-ordered cross-rank barriers.  That path makes no
-device-to-host read at all.  `exchange="nccl"` keeps the all-to-all form described above.
+With `exchange="fused"` (the default on CUDA tensors) steps 2-6 are three launches with no
+collective-library call and no device-to-host read: every rank holds a receive buffer and a
+return buffer in peer-mapped ("symmetric") memory; `tkmx_ep_exchange_plan` all-gathers the
+counts through peer stores, passes a bounded flag barrier and derives every offset of the step
+on the device; `tkmx_ep_moe_fused` is ONE kernel in which two warps of every CTA push this
+rank's token rows into the owners' receive buffers (plain stores over NVLink, expert by
+expert, with per-expert arrival counters) while the other warps multiply the experts whose
+rows have arrived and store each finished row straight into its source rank's return buffer;
+`tkmx_cross_rank_barrier` ends the step.  `exchange="nccl"` keeps the all-to-all form
+described above.
 
 `forward_with_residuals` / `backward` give the layer's gradients through the all-to-all
 exchange: cotangent rows travel to the experts' owners, dlhs rows travel back, drhs stays local.
@@ -88,16 +91,6 @@ class CudaBackend:
               top_k: int) -> torch.Tensor:
     return self._capi.moe_combine(rows, pos, gates.to(torch.float32).contiguous(), num_tokens, top_k)
 
-  def expert_gemm_into(self, rows, rhs_local, segment_sizes, out, begin: int = 0, count: int = -1):
-    """Grouped GEMM over a worst-case-sized receive buffer: rows past the received ones are
-    neither read for output nor zero-filled; only groups [begin, begin + count) are computed."""
-    self._capi.ragged_dot_fwd_cyclic(
-        rows, rhs_local, segment_sizes, out, zero_initialize=False, segment_begin=begin,
-        segment_count=count,
-        config=self._gemm_config(rows.shape[0] // max(1, segment_sizes.numel() // max(1, rhs_local.shape[0])),
-                                 segment_sizes.numel(), rhs_local.shape[2]))
-    return out
-
   def expert_gemm_dlhs(self, dout_rows: torch.Tensor, rhs_local: torch.Tensor, segment_sizes: torch.Tensor):
     """d(rows)[i, :] = dout_rows[i, :] @ rhs_local[expert(i)]^T over the same segments: the
     forward kernel with the weights read as stored ([G, K, N] is "[G, n_out, contraction]")."""
@@ -115,9 +108,6 @@ class CudaBackend:
     self._capi.ragged_dot_drhs(rows, dout_rows, segment_sizes, seg)
     return seg.reshape(-1, local_experts, rows.shape[1], dout_rows.shape[1]).sum(0)
 
-  def scatter_rows_p2p(self, src, src_row, dst_peer, dst_row, peer_base, capacity_rows, overflow_flag):
-    self._capi.moe_scatter_rows_p2p(src, src_row, dst_peer, dst_row, peer_base, capacity_rows, overflow_flag)
-
 
 @dataclasses.dataclass
 class DispatchPlan:
@@ -129,10 +119,13 @@ class DispatchPlan:
   segment_sizes: torch.Tensor   # int32 [W * G/W]: rows per (source rank, local expert)
   num_tokens: int
   top_k: int
+  local_group_sizes: torch.Tensor | None = None   # int32 [G/W] when the exchange computed it itself
 
   @property
   def group_sizes(self) -> torch.Tensor:
     """Rows per local expert (the column sums of the received [source, expert] counts)."""
+    if self.local_group_sizes is not None:
+      return self.local_group_sizes
     w = len(self.recv_splits)
     return self.segment_sizes.reshape(w, -1).sum(0).to(torch.int32)
 
@@ -153,7 +146,12 @@ class ExpertParallelMoE:
                num_chunks: int = 4, exchange: str | None = None):
     self.group = group
     self.num_chunks = num_chunks
-    self._p2p = None
+    self._fused = None
+    self._seq = 0
+    self.gemm_config = None          # a `_capi.Config` for the fused kernel's GEMM, or None for a size-based choice
+    self.timeout_ns = 2_000_000_000  # budget of every cross-rank flag wait
+    self.gemm_events = None          # set to a list to collect (start, end) CUDA events around the grouped GEMM
+    self.launches_last_call = 0      # kernels of this library launched by the last call
     self.world = dist.get_world_size(group) if dist.is_initialized() else 1
     self.rank = dist.get_rank(group) if dist.is_initialized() else 0
     if num_experts % self.world:
@@ -164,9 +162,11 @@ class ExpertParallelMoE:
       raise ValueError(f"rhs_local must hold {self.local_experts} experts, got {rhs_local.shape[0]}")
     self.rhs_local = rhs_local
     if exchange is None:
-      exchange = "p2p" if (self.world > 1 and backend is None and rhs_local.is_cuda) else "nccl"
-    if exchange not in ("p2p", "nccl"):
-      raise ValueError("exchange must be 'p2p' or 'nccl'")
+      exchange = "fused" if (backend is None and rhs_local.is_cuda) else "nccl"
+    if exchange not in ("fused", "nccl"):
+      raise ValueError("exchange must be 'fused' or 'nccl'")
+    if exchange == "fused" and backend is not None:
+      raise ValueError("the fused exchange runs on the CUDA kernels only")
     self.exchange = exchange
     if backend is None:
       # With overlapped NCCL exchanges, keep a few SMs free for the communication kernels.
@@ -226,13 +226,45 @@ class ExpertParallelMoE:
       self._all_to_all(ret, out_rows, plan.send_splits, plan.recv_splits)
     return self.backend.combine(ret, plan.pos, gates, plan.num_tokens, plan.top_k)
 
+  @property
+  def exchange_name(self) -> str:
+    if self.exchange == "fused":
+      return "fused (peer stores inside the GEMM kernel)"
+    return "nccl all-to-all" if self.world > 1 else "local (gather, GEMM, combine)"
+
+  @property
+  def gemm_kernel_name(self) -> str:
+    if self.exchange == "fused":
+      return "tkmx::ragged_gemm_kernel<kRowsBN, 256, pair, expert-parallel>"
+    return "tkmx::ragged_gemm_kernel<kRowsBN, 256, pair>"
+
+  def check_overflow(self) -> None:
+    """Raises if a kernel of an earlier call reported a problem (a timed-out cross-rank wait, a
+    row aimed outside a receive buffer).  Synchronises the device."""
+    from tokamax_b200 import _capi
+    _capi.device_status()
+
+  def _gemm_bracket(self):
+    """(start, end) events of the current stream when `gemm_events` collects them."""
+    if self.gemm_events is None:
+      return None
+    pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    self.gemm_events.append(pair)
+    return pair
+
   def __call__(self, tokens: torch.Tensor, expert_ids: torch.Tensor, gates: torch.Tensor):
-    if self.world > 1 and self.exchange == "p2p":
-      return self.forward_p2p(tokens, expert_ids, gates)
+    if self.exchange == "fused":
+      return self.forward_fused(tokens, expert_ids, gates)
     if self.world > 1 and self.num_chunks > 1:
       return self.forward_pipelined(tokens, expert_ids, gates)
     rows, plan = self.dispatch(tokens, expert_ids)
+    ev = self._gemm_bracket()
+    if ev:
+      ev[0].record()
     out_rows = self.backend.expert_gemm(rows, self.rhs_local, plan.segment_sizes)
+    if ev:
+      ev[1].record()
+    self.launches_last_call = 6     # 3 sort + gather + GEMM + combine
     return self.combine(out_rows, gates, plan), plan
 
   # ------------------------------------------------------------------ backward
@@ -341,135 +373,110 @@ class ExpertParallelMoE:
                         recv_counts.reshape(-1).to(torch.int32).contiguous(), t, top_k)
     return y, plan
 
-  # ------------------------------------------------------------------ peer-to-peer form
-  def _p2p_state(self, tokens: torch.Tensor, top_k: int):
-    """Peer-mapped buffers, allocated once per (token count, top_k): a receive buffer sized for
-    the worst case (every pair of every rank routed here) and a return buffer for this
-    rank's own pairs."""
-    import torch.distributed._symmetric_memory as symm_mem
+  # ------------------------------------------------------------------ fused form
+  def _fused_state(self, tokens: torch.Tensor, top_k: int):
+    """Buffers of the fused exchange, allocated once per (token count, top_k, row widths): the
+    receive buffer is sized for the worst case (every pair of every rank routed here), the
+    return buffer for this rank's own pairs.  With more than one rank they live in peer-mapped
+    ("symmetric") memory and every rank learns every rank's addresses."""
+    from tokamax_b200 import _capi
     t, k = tokens.shape
     n = self.rhs_local.shape[2]
     key = (t, top_k, k, n, tokens.dtype)
-    if self._p2p is not None and self._p2p["key"] == key:
-      return self._p2p
-    group = self.group if self.group is not None else dist.group.WORLD
+    if self._fused is not None and self._fused["key"] == key:
+      return self._fused
     dev = tokens.device
-    cap = self.world * t * top_k
-    recv = symm_mem.empty((cap, k), dtype=tokens.dtype, device=dev)
-    ret = symm_mem.empty((t * top_k, n), dtype=tokens.dtype, device=dev)
-    counts = symm_mem.empty((self.world, self.num_experts), dtype=torch.int32, device=dev)
-    recv_h = symm_mem.rendezvous(recv, group)
-    ret_h = symm_mem.rendezvous(ret, group)
-    counts_h = symm_mem.rendezvous(counts, group)
-    self._p2p = dict(
-        key=key, cap=cap, recv=recv, ret=ret, recv_h=recv_h, ret_h=ret_h, counts=counts, counts_h=counts_h,
-        counts_ptrs=torch.tensor(list(counts_h.buffer_ptrs), dtype=torch.int64, device=dev),
-        zeros_w=torch.zeros(self.world, dtype=torch.int32, device=dev),
-        peers_w=torch.arange(self.world, dtype=torch.int32, device=dev),
-        rank_w=torch.full((self.world,), self.rank, dtype=torch.int32, device=dev),
-        recv_ptrs=torch.tensor(list(recv_h.buffer_ptrs), dtype=torch.int64, device=dev),
-        ret_ptrs=torch.tensor(list(ret_h.buffer_ptrs), dtype=torch.int64, device=dev),
-        out=torch.empty((cap, n), dtype=tokens.dtype, device=dev),
-        overflow=torch.zeros(1, dtype=torch.int32, device=dev),
-        src_row=(torch.arange(t * top_k, device=dev, dtype=torch.int32) // top_k).contiguous(),
-        row_ids=torch.arange(cap, device=dev, dtype=torch.int64),
-        s_in=torch.cuda.Stream(device=dev), s_out=torch.cuda.Stream(device=dev))
-    return self._p2p
-
-  def forward_p2p(self, tokens: torch.Tensor, expert_ids: torch.Tensor, gates: torch.Tensor):
-    """dispatch -> GEMM -> combine with the rows moved by P2P stores; no host read and no
-    collective-library call.
-
-    1. every rank sorts its pairs and writes its per-expert counts into every peer's copy of
-       the [W, G] count matrix (P2P stores), then a cross-rank barrier;
-    2. from that matrix every rank derives, locally, where each of its pairs goes in the
-       owner's receive buffer -- laid out expert-major, (local expert, source rank), so the
-       rows of one expert are contiguous and form ONE group of the GEMM -- and where each
-       received row's output goes back in its source's sorted order;
-    3. scatter rows to the owners, barrier, grouped GEMM, scatter outputs back, barrier,
-       gate-weighted combine."""
-    st = self._p2p_state(tokens, expert_ids.shape[1])
-    t, top_k = expert_ids.shape
-    w, gl, g = self.world, self.local_experts, self.num_experts
-    i32, i64 = torch.int32, torch.int64
-    dev = tokens.device
-    pos, counts = self.backend.sort_pairs(expert_ids, g)            # counts int32 [G]
-    # all-gather of the counts through peer memory: row `rank` of everybody's matrix
-    self.backend.scatter_rows_p2p(counts.reshape(1, g), st["zeros_w"], st["peers_w"], st["rank_w"],
-                                  st["counts_ptrs"], w, st["overflow"])
-    st["counts_h"].barrier()        # counts are everywhere; everyone is done with the last call
-    allc = st["counts"].to(i64)                                      # [src, global expert]
-    send_off_all = torch.cumsum(allc, 1) - allc                      # [src, e]: src's first sorted pos of e
-    mine = allc[:, self.rank * gl:(self.rank + 1) * gl]              # [src, local e] rows I receive
-    # Receive layout on every owner: expert-major, sources in rank order inside an expert.
-    by_owner = allc.reshape(w, w, gl)                                # [src, owner, local e]
-    within = torch.cumsum(by_owner, 0) - by_owner                    # rows of earlier sources, same (owner, e)
-    per_expert = by_owner.sum(0)                                     # [owner, local e]
-    expert_start = torch.cumsum(per_expert, 1) - per_expert          # [owner, local e]
-    dst_off = (expert_start + within[self.rank]).reshape(-1)         # [global e]: where MY rows of e start
-    e = expert_ids.reshape(-1).to(i64)
-    dst_peer = (e // gl).to(i32)
-    dst_row = (dst_off[e] + pos - send_off_all[self.rank][e]).to(i32)
-    group_sizes = per_expert[self.rank].to(i32).contiguous()         # [local e]
-    # Output row r lies in segment (local e, src); it returns to src at the position its pair
-    # has in src's sorted order.
-    seg_sizes = mine.t().reshape(-1)                                 # [(local e, src)]
-    seg_end = torch.cumsum(seg_sizes, 0)
-    seg_start = seg_end - seg_sizes
-    ret_off = send_off_all[:, self.rank * gl:(self.rank + 1) * gl].t().reshape(-1)
-    r = st["row_ids"]
-    seg = torch.searchsorted(seg_end, r, right=True).clamp_(max=w * gl - 1)
-    back_peer = torch.where(r < seg_end[-1], seg % w, torch.full_like(seg, -1)).to(i32)
-    back_row = (ret_off[seg] + (r - seg_start[seg])).to(i32)
-    tokens = tokens.contiguous()
-
-    chunks = max(1, min(self.num_chunks, gl))
-    while gl % chunks:
-      chunks -= 1
-    if chunks == 1:
-      self.backend.scatter_rows_p2p(tokens, st["src_row"], dst_peer, dst_row,
-                                    st["recv_ptrs"], st["cap"], st["overflow"])
-      st["recv_h"].barrier()          # all rows have landed everywhere
-      out = self.backend.expert_gemm_into(st["recv"], self.rhs_local, group_sizes, st["out"])
-      self.backend.scatter_rows_p2p(out, None, back_peer, back_row, st["ret_ptrs"], t * top_k, st["overflow"])
-      st["ret_h"].barrier()           # all outputs are back
+    w, g, gl = self.world, self.num_experts, self.local_experts
+    if w > _capi.EP_MAX_WORLD:
+      raise NotImplementedError(f"the fused exchange serves up to {_capi.EP_MAX_WORLD} ranks")
+    pairs = t * top_k
+    cap = w * pairs
+    shapes = dict(recv=((cap, k), tokens.dtype), arrive=((gl,), torch.int32), ret=((pairs, n), tokens.dtype),
+                  counts=((w, g), torch.int32), flags=((w,), torch.int32))
+    bufs, ptrs = {}, {}
+    if w > 1:
+      import torch.distributed._symmetric_memory as symm_mem
+      group = self.group if self.group is not None else dist.group.WORLD
+      for name, (shape, dtype) in shapes.items():
+        bufs[name] = symm_mem.empty(shape, dtype=dtype, device=dev)
+        if name in ("arrive", "counts", "flags"):
+          bufs[name].zero_()
+        ptrs[name] = [int(p) for p in symm_mem.rendezvous(bufs[name], group).buffer_ptrs]
+      torch.cuda.synchronize(dev)
+      dist.barrier(group)     # every rank's flags are zero before anyone's first step
     else:
-      # Expert chunks: while chunk c is multiplied, chunk c+1 is still arriving (stream
-      # `s_in`) and the outputs of chunk c-1 are already leaving (stream `s_out`).
-      ce = gl // chunks
-      main = torch.cuda.current_stream()
-      s_in, s_out = st["s_in"], st["s_out"]
-      pair_chunk = (e % gl) // ce
-      row_chunk = (seg // w) // ce
-      minus1 = torch.full_like(dst_peer, -1)
-      minus1_rows = torch.full_like(back_peer, -1)
-      s_in.wait_stream(main)
-      s_out.wait_stream(main)
-      arrived = []
-      with torch.cuda.stream(s_in):
-        for c in range(chunks):
-          peer_c = torch.where(pair_chunk == c, dst_peer, minus1)
-          self.backend.scatter_rows_p2p(tokens, st["src_row"], peer_c, dst_row,
-                                        st["recv_ptrs"], st["cap"], st["overflow"])
-          st["recv_h"].barrier()      # chunk c has landed everywhere
-          ev = torch.cuda.Event()
-          ev.record(s_in)
-          arrived.append(ev)
-      for c in range(chunks):
-        main.wait_event(arrived[c])
-        out = self.backend.expert_gemm_into(st["recv"], self.rhs_local, group_sizes, st["out"],
-                                            begin=c * ce, count=ce)
-        done = torch.cuda.Event()
-        done.record(main)
-        with torch.cuda.stream(s_out):
-          s_out.wait_event(done)
-          peer_c = torch.where(row_chunk == c, back_peer, minus1_rows)
-          self.backend.scatter_rows_p2p(out, None, peer_c, back_row, st["ret_ptrs"], t * top_k,
-                                        st["overflow"])
-      with torch.cuda.stream(s_out):
-        st["ret_h"].barrier()         # all outputs are back
-      main.wait_stream(s_in)
-      main.wait_stream(s_out)
-    y = self.backend.combine(st["ret"], pos, gates, t, top_k)
-    plan = DispatchPlan(pos, [], [0] * w, mine.reshape(-1).to(i32), t, top_k)
+      for name, (shape, dtype) in shapes.items():
+        bufs[name] = torch.zeros(shape, dtype=dtype, device=dev) if name != "recv" else torch.empty(
+            shape, dtype=dtype, device=dev)
+        ptrs[name] = [bufs[name].data_ptr()]
+    table = torch.zeros((5, _capi.EP_MAX_WORLD), dtype=torch.int64)
+    for row, name in ((_capi.EP_TAB_RECV, "recv"), (_capi.EP_TAB_ARRIVE, "arrive"), (_capi.EP_TAB_RET, "ret"),
+                      (_capi.EP_TAB_COUNTS, "counts"), (_capi.EP_TAB_FLAGS, "flags")):
+      for r in range(w):
+        # addresses above 2^63 would not fit int64: CUDA virtual addresses are far below
+        table[row, r] = ptrs[name][r]
+    self._fused = dict(
+        key=key, cap=cap, bufs=bufs, table=table.to(dev),
+        plan=torch.zeros(_capi.ep_plan_ints(g, w), dtype=torch.int32, device=dev),
+        pos=torch.empty(pairs, dtype=torch.int32, device=dev),
+        sorted_pair=torch.zeros(pairs, dtype=torch.int32, device=dev),
+        my_counts=torch.empty(g, dtype=torch.int32, device=dev),
+        sort_ws=torch.empty(max(_capi.moe_sort_workspace_bytes(pairs, g), 4), dtype=torch.uint8, device=dev))
+    return self._fused
+
+  def _fused_config(self, pairs: int):
+    from tokamax_b200 import _capi
+    if self.gemm_config is not None:
+      return self.gemm_config
+    # CTA pairs (256-row tiles) once the average expert fills most of a pair tile.
+    mean_rows = pairs * self.world / max(self.local_experts, 1)
+    return _capi.Config(collective=1 if mean_rows >= 192 else 0)
+
+  def forward_fused(self, tokens: torch.Tensor, expert_ids: torch.Tensor, gates: torch.Tensor,
+                    phases: tuple[int, ...] = (3,)):
+    """sort -> counts exchange + plan -> ONE kernel that sends this rank's rows, multiplies what
+    has arrived and returns finished rows -> barrier -> gate-weighted combine.  Seven launches,
+    no host read, no collective-library call.
+
+    The returned plan's `pos` aliases a buffer that the next call overwrites.  `phases` splits
+    the fused kernel into launches of its parts, (1, 2) = send everything, then multiply (a
+    cross-rank barrier is put between them): the form the tests use to tell the two halves
+    apart."""
+    from tokamax_b200 import _capi
+    if not tokens.is_cuda:
+      raise NotImplementedError("the fused exchange runs on CUDA tensors only (no CPU fallback)")
+    t, top_k = expert_ids.shape
+    st = self._fused_state(tokens, top_k)
+    w, g = self.world, self.num_experts
+    b = st["bufs"]
+    ids = expert_ids.reshape(-1)
+    if ids.dtype != torch.int32:
+      ids = ids.to(torch.int32)
+    tokens = tokens.contiguous()
+    _capi.moe_sort_pairs_inverse(ids.contiguous(), g, st["pos"], st["sorted_pair"], st["my_counts"], st["sort_ws"])
+    self._seq += 1
+    _capi.ep_exchange_plan(st["my_counts"], st["table"], b["counts"], b["flags"], b["arrive"], st["plan"], g, w,
+                           self.rank, self._seq, self.timeout_ns)
+    cfg = self._fused_config(t * top_k)
+    n = self.rhs_local.shape[2]
+    launches = 3 + 1
+    ev = self._gemm_bracket()
+    if ev:
+      ev[0].record()
+    for i, ph in enumerate(phases):
+      if i > 0:
+        self._seq += 1
+        _capi.cross_rank_barrier(st["table"], b["flags"], w, self.rank, self._seq, self.timeout_ns)
+        launches += 1
+      _capi.ep_moe_fused(tokens, st["sorted_pair"], b["recv"], self.rhs_local, st["plan"], st["table"],
+                         b["arrive"], top_k, g, w, self.rank, n, phases=ph, config=cfg)
+      launches += 1
+    if ev:
+      ev[1].record()
+    self._seq += 1
+    _capi.cross_rank_barrier(st["table"], b["flags"], w, self.rank, self._seq, self.timeout_ns)
+    y = self.backend.combine(b["ret"], st["pos"], gates, t, top_k)
+    self.launches_last_call = launches + 2
+    plan = DispatchPlan(st["pos"], [], [0] * w, st["plan"][:0], t, top_k,
+                        local_group_sizes=st["plan"][:self.local_experts])
     return y, plan
