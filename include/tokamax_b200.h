@@ -50,6 +50,16 @@ typedef enum tkmx_dtype {
   TKMX_S8 = 4      /* weights only, with per-output-channel fp32 scales */
 } tkmx_dtype;
 
+/* Elementwise activations of tkmx_ragged_dot_fwd_epilogue (codes 1-4 are its gate/up forms). */
+enum {
+  TKMX_ACT_RELU = 16,
+  TKMX_ACT_SILU = 17,
+  TKMX_ACT_GELU_TANH = 18,
+  TKMX_ACT_GELU_ERF = 19,
+  TKMX_ACT_TANH = 20,
+  TKMX_ACT_SIGMOID = 21
+};
+
 /* Storage order of the grouped right-hand side of the forward product. */
 typedef enum tkmx_rhs_layout {
   TKMX_RHS_GKN = 0, /* rhs[g, k, n], n contiguous: the reference's logical layout */
@@ -130,8 +140,11 @@ TKMX_API int tkmx_ragged_dot_fwd_gateup(const void* lhs, const void* rhs, const 
 
 /*
  * Forward with an epilogue: tmp = ragged_dot(lhs, rhs) + rhs_bias[group] (rows of no group
- * stay zero), then either out = tmp (activation 0) or the gate/up activation of
- * tkmx_ragged_dot_fwd_gateup on tmp (activation 1-4, rhs_layout GKN only, out [m, n/2]).
+ * stay zero), then either out = tmp (activation 0), or the gate/up activation of
+ * tkmx_ragged_dot_fwd_gateup on tmp (activation 1-4, rhs_layout GKN only, out [m, n/2]), or an
+ * elementwise activation of tmp computed in float32 before the cast to out_dtype (activation
+ * TKMX_ACT_RELU ... TKMX_ACT_SIGMOID, 16-bit weights only): the `activation=` argument of
+ * ragged_dot (tokamax/_src/ops/ragged_dot/api.py:84,108-113).
  *   rhs_scale  float[g, n] with F8E4M3 weights (then the workspace of
  *              tkmx_ragged_dot_workspace_bytes is required: the epilogue extras live in the
  *              native fp8 kernel; n/2 must be a multiple of 16 for the gate/up form), else NULL

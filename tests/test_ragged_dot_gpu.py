@@ -106,7 +106,7 @@ def test_zero_group_sizes_all_patterns(capi):
       capi.ragged_dot_drhs(dl, dd, gsd, drhs)
       want_dlhs, want_drhs = ref.ragged_dot_vjp_ref(lhs, rhs, gs, dout)
       helpers.assert_close(dlhs, want_dlhs, what=f"dlhs gs={gs.tolist()}")
-      helpers.assert_close(drhs, want_drhs, atol=5e-2, what=f"drhs gs={gs.tolist()}")
+      helpers.assert_close(drhs, want_drhs, what=f"drhs gs={gs.tolist()}")
   capi.device_status()
 
 
@@ -134,7 +134,7 @@ def test_ragged_patterns_all_ops(capi, pattern, block_n, collective):
                        ref.ragged_dot_ref(lhs, rhs, gs), what="fwd rhs[g,n,k]")
   want_dlhs, want_drhs = ref.ragged_dot_vjp_ref(lhs, rhs, gs, dout)
   helpers.assert_close(_dlhs(capi, dout, rhs, gs, **cfg), want_dlhs, what="dlhs")
-  helpers.assert_close(_drhs(capi, lhs, dout, gs, **cfg), want_drhs, atol=5e-2, what="drhs")
+  helpers.assert_close(_drhs(capi, lhs, dout, gs, **cfg), want_drhs, what="drhs")
 
 
 @pytest.mark.parametrize("collective", [0, 1])
@@ -148,7 +148,7 @@ def test_unaligned_tails(capi, shape, collective):
   helpers.assert_close(_fwd(capi, lhs, rhs, gs, **cfg), ref.ragged_dot_ref(lhs, rhs, gs), what="fwd")
   want_dlhs, want_drhs = ref.ragged_dot_vjp_ref(lhs, rhs, gs, dout)
   helpers.assert_close(_dlhs(capi, dout, rhs, gs, **cfg), want_dlhs, what="dlhs")
-  helpers.assert_close(_drhs(capi, lhs, dout, gs, **cfg), want_drhs, atol=5e-2, what="drhs")
+  helpers.assert_close(_drhs(capi, lhs, dout, gs, **cfg), want_drhs, what="drhs")
 
 
 @pytest.mark.parametrize("collective", [0, 1])
@@ -163,7 +163,7 @@ def test_config_space_is_numerically_neutral(capi, stages, minor, width, collect
   helpers.assert_close(_fwd(capi, lhs, rhs, gs, **cfg), ref.ragged_dot_ref(lhs, rhs, gs), what="fwd")
   want_dlhs, want_drhs = ref.ragged_dot_vjp_ref(lhs, rhs, gs, dout)
   helpers.assert_close(_dlhs(capi, dout, rhs, gs, **cfg), want_dlhs, what="dlhs")
-  helpers.assert_close(_drhs(capi, lhs, dout, gs, **cfg), want_drhs, atol=5e-2, what="drhs")
+  helpers.assert_close(_drhs(capi, lhs, dout, gs, **cfg), want_drhs, what="drhs")
 
 
 @pytest.mark.parametrize("out_type", [None, torch.bfloat16, torch.float32])
@@ -233,7 +233,7 @@ def test_against_committed_goldens(capi):
     gs = gold[f"{name}.group_sizes"]
     helpers.assert_close(_fwd(capi, lhs, rhs, gs), gold[f"{name}.fwd"], what=f"{name} fwd")
     helpers.assert_close(_dlhs(capi, dout, rhs, gs), gold[f"{name}.dlhs"], what=f"{name} dlhs")
-    helpers.assert_close(_drhs(capi, lhs, dout, gs), gold[f"{name}.drhs"], atol=5e-2, what=f"{name} drhs")
+    helpers.assert_close(_drhs(capi, lhs, dout, gs), gold[f"{name}.drhs"], what=f"{name} drhs")
 
 
 def test_relaunch_is_bit_identical(capi):
@@ -284,14 +284,16 @@ def _f8_workspace(capi, m, k, n, g):
 
 
 @pytest.mark.parametrize("qdtype,native", [(torch.float8_e4m3fn, False), (torch.float8_e4m3fn, True),
-                                           (torch.int8, False)], ids=["fp8", "fp8native", "int8"])
+                                           (torch.int8, False), (torch.int8, True)],
+                         ids=["fp8", "fp8native", "int8", "int8native"])
 @pytest.mark.parametrize("block_n,collective", [(128, 0), (256, 0), (256, 1)])
 @pytest.mark.parametrize("pattern", [(33, 67, 50, 80, 70, 60, 90, 62), (0, 130, 0, 200, 0, 98, 84, 0),
                                      (1, 7, 199, 1, 100, 50, 151, 3), (700,)])
 def test_quantized_weights(capi, qdtype, native, block_n, collective, pattern):
   """fp8-e4m3 / int8 weights with one fp32 scale per (expert, output channel): the kernel
   against dequantise-then-dot on the SAME (q, scale), tolerance 5e-2.  `native` passes the
-  workspace that selects the fp8 tensor-core kernel (activations split into two e4m3 terms)."""
+  workspace that selects the 8-bit tensor-core kernel (activations split into two e4m3 terms
+  for fp8 weights, into two int8 terms for int8 weights)."""
   g = len(pattern)
   m, k, n = 768, 448, 384
   rng = np.random.default_rng(sum(str(pattern).encode()))
@@ -313,7 +315,8 @@ def test_quantized_weights(capi, qdtype, native, block_n, collective, pattern):
 
 
 @pytest.mark.parametrize("qdtype,native", [(torch.float8_e4m3fn, False), (torch.float8_e4m3fn, True),
-                                           (torch.int8, False)], ids=["fp8", "fp8native", "int8"])
+                                           (torch.int8, False), (torch.int8, True)],
+                         ids=["fp8", "fp8native", "int8", "int8native"])
 def test_quantized_every_code_point(capi, qdtype, native):
   """Every 8-bit code (fp8: all 254 finite encodings incl. subnormals; int8: -128..127) is
   expanded exactly: with lhs = identity rows the output reproduces q * scale.  (Native fp8
@@ -335,7 +338,11 @@ def test_quantized_every_code_point(capi, qdtype, native):
                       workspace=_f8_workspace(capi, 128, k, n, 1) if native else None)
   capi.device_status()
   want = lhs.float() @ q[0].float()
-  assert torch.equal(out.cpu(), want)
+  if native and qdtype == torch.int8:
+    # the int8 split's row scale is max|a| / 127, not a power of two: one rounding of 127 * s
+    torch.testing.assert_close(out.cpu(), want, rtol=1e-6, atol=1e-5)
+  else:
+    assert torch.equal(out.cpu(), want)
 
 
 @pytest.mark.parametrize("collective", [0, 1])
@@ -982,8 +989,9 @@ def test_cfg3_deepseek_fp8_full_size_properties(capi, tk):
 
 
 def test_cfg4_qwen_backward_full_size(capi):
-  """dlhs and drhs at full size: sampled groups against the oracle, and drhs == sum over
-  a split of the group (additivity over the contraction)."""
+  """dlhs and drhs at full size, every one of the 128 groups: against per-group float32
+  products (computed on the device in true float32, TF32 off) within 2e-2 + 2e-2*|x|; four
+  groups also against the same products on the host."""
   from tokamax_b200.ragged_dot import arg_specs
   w = arg_specs.workload("cfg4")
   gen = torch.Generator(device="cuda").manual_seed(1)
@@ -1002,7 +1010,21 @@ def test_cfg4_qwen_backward_full_size(capi):
     want_dl = dout[lo:hi].float().cpu() @ rhs[gi].float().cpu().T
     helpers.assert_close(dlhs[lo:hi], want_dl, what=f"dlhs group {gi}")
     want_dr = lhs[lo:hi].float().cpu().T @ dout[lo:hi].float().cpu()
-    helpers.assert_close(drhs[gi], want_dr, atol=0.25, rtol=2e-2, what=f"drhs group {gi}")
+    helpers.assert_close(drhs[gi], want_dr, what=f"drhs group {gi}")
+  tf32 = torch.backends.cuda.matmul.allow_tf32
+  torch.backends.cuda.matmul.allow_tf32 = False
+  try:
+    worst = 0.0
+    for gi in range(w.g):
+      lo, hi = int(off[gi]), int(off[gi + 1])
+      want_dl = dout[lo:hi].float() @ rhs[gi].float().T
+      want_dr = lhs[lo:hi].float().T @ dout[lo:hi].float()
+      for got, want in ((dlhs[lo:hi], want_dl), (drhs[gi], want_dr)):
+        ratio = ((got.float() - want).abs() / (helpers.BF16_ATOL + helpers.BF16_RTOL * want.abs())).max().item()
+        worst = max(worst, ratio)
+    assert worst <= 1.0, f"worst error / tolerance over all groups: {worst}"
+  finally:
+    torch.backends.cuda.matmul.allow_tf32 = tf32
 
 
 # ---------------------------------------------------------------- host-buffer pipeline
@@ -1111,3 +1133,90 @@ def test_ragged_gather_reduce(group):
   with pytest.raises(ValueError):
     rg.ragged_gather_reduce(x.cuda(), torch.from_numpy(idx).cuda(), torch.from_numpy(w).cuda(),
                             torch.from_numpy(mask).cuda(), reduce_group_size=7)
+
+
+# ---------------------------------------------------------------- fused `activation=`
+@pytest.mark.parametrize("collective", [0, 1])
+@pytest.mark.parametrize("name", ["relu", "silu", "gelu_tanh", "gelu_erf", "tanh", "sigmoid"])
+def test_fused_elementwise_activation(capi, name, collective):
+  """`activation=` computed on the float32 accumulator inside the kernel
+  (tokamax/_src/ops/ragged_dot/api.py:108-113): every store path (TMA-stored full blocks,
+  predicated ragged blocks, swapped short tiles, zero-fill rows) against act(float32 product)."""
+  import torch.nn.functional as F
+  g, m, k, n = 5, 1400, 160, 520
+  rng = np.random.default_rng(sum(name.encode()) + collective)
+  lhs = torch.from_numpy(rng.normal(0, 1, (m, k)).astype(np.float32)).bfloat16()
+  rhs = torch.from_numpy(rng.normal(0, k ** -0.5, (g, k, n)).astype(np.float32)).bfloat16()
+  gs = np.array([512, 0, 300, 40, 415], np.int32)          # 133 trailing rows of no group
+  fns = {"relu": torch.relu, "silu": F.silu, "gelu_tanh": lambda x: F.gelu(x, approximate="tanh"),
+         "gelu_erf": F.gelu, "tanh": torch.tanh, "sigmoid": torch.sigmoid}
+  out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+  capi.ragged_dot_fwd_epilogue(lhs.cuda(), rhs.cuda(), _gs_dev(gs), out, element_activation=name,
+                               config=capi.Config(block_n=256, collective=collective))
+  capi.device_status()
+  pre = ref.ragged_dot_ref(lhs, rhs, gs, out_dtype=torch.float32)
+  helpers.assert_close(out, fns[name](pre), what=f"fused {name}")
+
+
+def test_activation_argument_is_fused_when_recognised(tk, capi):
+  """Through the public call: a recognised callable runs inside the kernel (bit-equal to the
+  epilogue entry point), an unknown one is applied after the kernel, and with
+  return_residuals the kernel is left unfused (the residual is the pre-activation result)."""
+  import torch.nn.functional as F
+  from tokamax_b200.ragged_dot import api
+  from tokamax_b200.ragged_dot import b200 as b200_lib
+  g, m, k, n = 4, 640, 128, 256
+  lhs, rhs, _, _ = helpers.seeded_inputs("fused-act", m, k, n, g, scale=0.3)
+  gs = np.array([200, 100, 40, 300], np.int32)
+  gsd = _gs_dev(gs)
+  got = tk.ragged_dot(lhs.cuda(), rhs.cuda(), gsd, activation=F.silu)
+  bound = b200_lib.B200RaggedDot().bind(lhs.cuda(), rhs.cuda(), group_sizes=gsd)
+  direct = torch.empty_like(got)
+  capi.ragged_dot_fwd_epilogue(lhs.cuda(), rhs.cuda(), gsd, direct, element_activation="silu",
+                               config=bound.default_config.to_capi())
+  assert torch.equal(got, direct)
+  pre = ref.ragged_dot_ref(lhs, rhs, gs, out_dtype=torch.float32)
+  helpers.assert_close(got, F.silu(pre), what="activation=silu")
+  odd = lambda x: x * 2 + 1
+  helpers.assert_close(tk.ragged_dot(lhs.cuda(), rhs.cuda(), gsd, activation=odd), odd(pre.bfloat16().float()),
+                       what="unknown callable, applied after the kernel")
+  assert b200_lib.fusable_activation(odd) is None
+  op = api.IMPLEMENTATIONS["b200"]
+  out, res = op(lhs.cuda(), rhs.cuda(), group_sizes=gsd, activation=torch.relu, return_residuals=True)
+  helpers.assert_close(res, pre, what="residuals are the pre-activation product")
+  assert torch.equal(out, torch.relu(res))
+
+
+def test_two_launches_on_one_tile_counter_word_report_a_conflict(capi, monkeypatch):
+  """Dynamic scheduling hands every launch one of a fixed set of tile-counter words.  If two
+  launches that overlap on the device are given the same word, neither may silently skip
+  tiles: the one that sees the other's epoch stops and the status word reports it."""
+  monkeypatch.setenv("TKMX_SCHED_SLOT", "7")
+  monkeypatch.setenv("TKMX_DYNAMIC", "1")
+  g, m, k, n = 8, 16384, 1024, 2048
+  gen = torch.Generator(device="cuda").manual_seed(3)
+  lhs = torch.randn(m, k, device="cuda", generator=gen).bfloat16()
+  rhs = (torch.randn(g, k, n, device="cuda", generator=gen) * k ** -0.5).bfloat16()
+  gsd = _gs_dev([m // g] * g)
+  outs = [torch.zeros(m, n, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+  streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+  cfg = capi.Config(block_n=256, collective=0, max_ctas=64)     # both launches fit on the device together
+  capi.device_status()
+  torch.cuda.synchronize()
+  for _ in range(4):
+    for s, o in zip(streams, outs):
+      with torch.cuda.stream(s):
+        capi.ragged_dot_fwd(lhs, rhs, gsd, o, config=cfg)
+  torch.cuda.synchronize()
+  monkeypatch.delenv("TKMX_SCHED_SLOT")
+  want = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+  conflict = False
+  try:
+    capi.device_status()
+  except RuntimeError as e:
+    assert "tile-counter word" in str(e)
+    conflict = True
+  capi.ragged_dot_fwd(lhs, rhs, gsd, want, config=cfg)
+  capi.device_status()                                           # the device keeps working
+  if not conflict:     # the launches happened not to overlap: then both results must be complete
+    assert torch.equal(outs[0], want) and torch.equal(outs[1], want)

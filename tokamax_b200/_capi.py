@@ -240,6 +240,9 @@ def ragged_dot_fwd(lhs, rhs, group_sizes, out, *, rhs_scale=None, rhs_layout=RHS
 
 
 GATEUP_ACTIVATIONS = {"silu": 1, "gelu": 2, "gelu_tanh": 2, "swigluoai": 3, "silu_and_mul_with_clamp": 4}
+# Elementwise activations the epilogue applies to the float32 result (TKMX_ACT_* of the header).
+ELEMENT_ACTIVATIONS = {"relu": 16, "silu": 17, "swish": 17, "gelu_tanh": 18, "gelu": 19, "gelu_erf": 19,
+                       "tanh": 20, "sigmoid": 21}
 
 
 def ragged_dot_fwd_gateup(lhs, rhs, group_sizes, out, activation: str, *, config: Config | None = None) -> None:
@@ -257,14 +260,20 @@ def ragged_dot_fwd_gateup(lhs, rhs, group_sizes, out, activation: str, *, config
 
 
 def ragged_dot_fwd_epilogue(lhs, rhs, group_sizes, out, *, rhs_scale=None, rhs_bias=None,
-                            activation: str | None = None, rhs_layout=RHS_GKN, config: Config | None = None,
-                            workspace=None) -> None:
+                            activation: str | None = None, element_activation: str | None = None,
+                            rhs_layout=RHS_GKN, config: Config | None = None, workspace=None) -> None:
   """out = ragged_dot(lhs, rhs) [* rhs_scale] + rhs_bias[group], optionally followed by the
-  fused gate/up activation (out then has n/2 columns).  rhs_scale / rhs_bias: float32 [g, n]
-  or None; 8-bit rhs needs the workspace of `workspace_bytes`."""
+  fused gate/up activation `activation` (out then has n/2 columns) or by the elementwise
+  `element_activation` (a key of ELEMENT_ACTIVATIONS), both computed in float32.  rhs_scale /
+  rhs_bias: float32 [g, n] or None; 8-bit rhs needs the workspace of `workspace_bytes`."""
   dev = _require_cuda(lhs, rhs, group_sizes, out, rhs_scale, rhs_bias, workspace)
   if activation is not None and activation not in GATEUP_ACTIVATIONS:
     raise NotImplementedError(f"Unsupported activation function: {activation}")
+  if element_activation is not None:
+    if activation is not None:
+      raise NotImplementedError("a gate/up activation and an elementwise one cannot both be fused")
+    if element_activation not in ELEMENT_ACTIVATIONS:
+      raise NotImplementedError(f"Unsupported activation function: {element_activation}")
   for t, what in ((rhs_bias, "rhs_bias"), (rhs_scale, "rhs_scale")):
     if t is not None and t.dtype != torch.float32:
       raise ValueError(f"{what} must be float32")
@@ -276,7 +285,8 @@ def ragged_dot_fwd_epilogue(lhs, rhs, group_sizes, out, *, rhs_scale=None, rhs_b
         _ptr(lhs), _ptr(rhs), _ptr(group_sizes), _ptr(rhs_scale), _ptr(rhs_bias), _ptr(out), _ptr(workspace),
         0 if workspace is None else workspace.numel() * workspace.element_size(), m, k, n, g,
         dtype_code(lhs.dtype), dtype_code(rhs.dtype), dtype_code(out.dtype), rhs_layout,
-        0 if activation is None else GATEUP_ACTIVATIONS[activation], _cfg(config), _stream(dev))
+        ELEMENT_ACTIVATIONS[element_activation] if element_activation is not None
+        else (0 if activation is None else GATEUP_ACTIVATIONS[activation]), _cfg(config), _stream(dev))
   check(st, "tkmx_ragged_dot_fwd_epilogue")
 
 

@@ -282,7 +282,7 @@ __device__ __forceinline__ void ep_send_rows(const EpFusedParams& ep, const int*
   const EpPlanLayout L = ep_plan_layout(G, W);
   const int P = s_vstart[G];
   const int num_items = (P + kEpItemRows - 1) / kEpItemRows;
-  constexpr int kU = 7;   // 16-byte pieces in flight per lane
+  constexpr int kU = 14;  // 16-byte pieces in flight per lane (7 KiB per warp)
   for (int item = sender; item < num_items; item += num_senders) {
     const int i = item * kEpItemRows + lane;
     bool act = lane < kEpItemRows && i < P;

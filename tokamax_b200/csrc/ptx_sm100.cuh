@@ -311,6 +311,31 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64
   }
 }
 
+// kind::i8: signed / unsigned 8-bit integer inputs, int32 accumulation, K = 32 per instruction.
+template <int kCtaGroup>
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                        uint32_t idesc, uint32_t accumulate) {
+  if constexpr (kCtaGroup == 1) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
 // Make the mbarrier track completion of all UMMAs this thread issued so far.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -381,6 +406,15 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_format, uint32_t b_
          | (b_mn_major << 16)          // [16]    B major
          | ((umma_n >> 3) << 17)       // [17,23) N / 8
          | ((umma_m >> 4) << 24);      // [24,29) M / 16
+}
+
+// Instruction descriptor for kind::i8 with signed 8-bit inputs and int32 accumulation.
+__host__ __device__ constexpr uint32_t make_idesc_s8(uint32_t a_mn_major, uint32_t b_mn_major,
+                                                     uint32_t umma_m, uint32_t umma_n) {
+  return (2u << 4)                     // [4,6)   D format = S32
+         | (1u << 7)                   // [7,10)  A format = signed 8-bit
+         | (1u << 10)                  // [10,13) B format = signed 8-bit
+         | (a_mn_major << 15) | (b_mn_major << 16) | ((umma_n >> 3) << 17) | ((umma_m >> 4) << 24);
 }
 
 }  // namespace ptx

@@ -238,8 +238,9 @@ int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& 
     if (st != TKMX_OK) return st;
   }
   cudaLaunchConfig_t cfg = {};
+  constexpr int kThreads = kEp ? tkmx::kEpNumThreads : tkmx::kNumThreads;
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(tkmx::kNumThreads, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -259,7 +260,7 @@ int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& 
       fit = clusters * 2;
     } else {
       int per_sm = 0, dev = 0, sms = 0;
-      TKMX_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, tkmx::kNumThreads, smem));
+      TKMX_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem));
       TKMX_CUDA_OK(cudaGetDevice(&dev));
       TKMX_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
       fit = per_sm * sms;
@@ -329,6 +330,14 @@ int run_rows(const void* a, const void* b, bool b_cols_contiguous, const int32_t
              cudaStream_t stream, bool zero_initialize = true, int64_t group_begin = 0,
              int64_t group_count = -1, int gateup = 0, const float* col_bias = nullptr) {
   if (g_rhs <= 0 && g > 0) return TKMX_ERR_INVALID_ARGUMENT;
+  // Codes from TKMX_ACT_RELU up are elementwise activations on the float32 result; the codes
+  // below them are the gate/up forms.
+  int element_act = 0;
+  if (gateup >= TKMX_ACT_RELU) {
+    if (gateup > TKMX_ACT_SIGMOID) return TKMX_ERR_INVALID_ARGUMENT;
+    element_act = gateup - TKMX_ACT_RELU + 1;
+    gateup = 0;
+  }
   if (gateup != 0) {
     // act(gate) * up over the two halves of the weight columns: [G, K, N] weights only, and
     // tiles whose halves are whole 64-column boxes.
@@ -352,6 +361,7 @@ int run_rows(const void* a, const void* b, bool b_cols_contiguous, const int32_t
   if (out == nullptr) return TKMX_ERR_INVALID_ARGUMENT;
   const size_t out_bytes = size_t(m) * size_t(gateup ? cols / 2 : cols) * elt_size(out_dtype);
   if (g == 0 || cdim == 0) {
+    if (element_act == tkmx::kActSigmoid) return TKMX_ERR_UNSUPPORTED;   // sigmoid(0) = 0.5: not a memset
     TKMX_CUDA_OK(cudaMemsetAsync(out, 0, out_bytes, stream));
     return TKMX_OK;
   }
@@ -405,6 +415,7 @@ int run_rows(const void* a, const void* b, bool b_cols_contiguous, const int32_t
   if ((reinterpret_cast<uintptr_t>(col_bias) & 3u) != 0) return TKMX_ERR_ALIGNMENT;
   const int64_t out_cols = gateup ? cols / 2 : cols;
   p.gateup = gateup;
+  p.activation = element_act;
   p.out_vec_ok = ((out_cols * elt_size(out_dtype)) % 16 == 0) &&
                  ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
   const uint32_t fmt_a = in_dtype == TKMX_BF16 ? 1u : 0u;
@@ -420,6 +431,10 @@ int run_rows(const void* a, const void* b, bool b_cols_contiguous, const int32_t
   // swapped MMA operands (cost follows its rows).  192 = where the swapped MMA stops being
   // cheaper than the full one (measured 141 against 173 cycles).  TKMX_SWAP_ROWS overrides.
   p.swap_rows = (rc.pair && rc.block_n == 256 && !gateup) ? env_int("TKMX_SWAP_ROWS", 192, 0, 192) : 0;
+  // Equal swapped tiles instead of full + short ones: off by default.  Measured on B200 it
+  // lost (cfg4: 0.40 against 0.24 ms): a swapped tile's transposed epilogue stores 2 bytes per
+  // lane and grows with the tile's rows, which outweighs the MMA time saved.
+  p.balance_tiles = env_int("TKMX_BALANCE_TILES", 0, 0, 1);
 
   // 16-bit outputs: blocks of 32 rows x 64 columns that are not ragged leave by TMA store.
   CUtensorMap mo = {};
@@ -467,10 +482,10 @@ int launch_w8(const CUtensorMap& ma, const CUtensorMap& mb, const RaggedGemmPara
   return TKMX_OK;
 }
 
-template <int kBlockN, bool kPair>
+template <int kBlockN, bool kPair, bool kInt8 = false>
 int launch_f8(const CUtensorMap& ma, const CUtensorMap& ma32, const CUtensorMap& mb,
               const RaggedGemmParams& p, const float* row_scale, int grid, cudaStream_t stream) {
-  auto kernel = tkmx::ragged_gemm_f8_kernel<kBlockN, kPair>;
+  auto kernel = tkmx::ragged_gemm_f8_kernel<kBlockN, kPair, kInt8>;
   const int smem = tkmx::make_f8_smem_layout(kBlockN, kPair, p.num_stages, p.num_groups).total + 1024;
   {
     const int st = raise_smem_limit(kernel, smem);
@@ -504,7 +519,7 @@ int f8_swap_rows() { return env_int("TKMX_F8_SWAP_ROWS", 64, 0, 64); }
 int f8_prefetch_blocks() { return env_int("TKMX_F8_PREFETCH", 0, 0, 64); }
 
 bool f8_native_usable(int rhs_dtype, const void* workspace, size_t workspace_bytes, int64_t m, int64_t k) {
-  return rhs_dtype == TKMX_F8E4M3 && workspace != nullptr && k % 16 == 0 &&
+  return (rhs_dtype == TKMX_F8E4M3 || rhs_dtype == TKMX_S8) && workspace != nullptr && k % 16 == 0 &&
          (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 &&
          workspace_bytes >= tkmx::f8_workspace(m, k).total;
 }
@@ -562,6 +577,7 @@ int run_rows_w8(const void* lhs, const void* rhs8, const int32_t* group_sizes, c
     // Epilogue extras exist in the native fp8 kernel only, on 256-column tiles whose gate and
     // up halves start on 16-byte boundaries of the 8-bit rows.
     if (!native_f8 || gateup < 0 || gateup > tkmx::kGateUpSiluClamp) return TKMX_ERR_UNSUPPORTED;
+    if (gateup != 0 && rhs_dtype == TKMX_S8) return TKMX_ERR_UNSUPPORTED;   // int8: plain and bias epilogues only
     if (gateup != 0 && (n % 2 != 0 || (n / 2) % 16 != 0 || rc.block_n != 256)) return TKMX_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(col_bias) & 3u) != 0) return TKMX_ERR_ALIGNMENT;
   }
@@ -648,6 +664,22 @@ int run_rows_w8(const void* lhs, const void* rhs8, const int32_t* group_sizes, c
     int32_t* sched = reinterpret_cast<int32_t*>(planes + ws.sched_off);
     const __nv_bfloat16* a16 = static_cast<const __nv_bfloat16*>(lhs);
     uint8_t* lo_plane = planes + ws.plane_bytes;
+    if (rhs_dtype == TKMX_S8) {
+      // int8 weights: int8 activation planes, kind::i8 MMAs, two int32 accumulators per tile.
+      if (k <= 4096)
+        tkmx::split_rows_s8_kernel<16><<<split_blocks, 256, 0, stream>>>(a16, planes, lo_plane, row_scale, sched, int(m), int(k));
+      else
+        tkmx::split_rows_s8_kernel<28><<<split_blocks, 256, 0, stream>>>(a16, planes, lo_plane, row_scale, sched, int(m), int(k));
+      TKMX_CUDA_OK(cudaGetLastError());
+      p.idesc = tkmx::ptx::make_idesc_s8(0u, 1u, rc.pair ? 256u : 128u, uint32_t(rc.block_n));
+      p.swap_rows = rc.pair ? 0 : f8_swap_rows();
+      p.prefetch_blocks = 0;
+      p.mixed_order = 0;
+      p.sched_counter = (!rc.pair && env_int("TKMX_F8_DYNAMIC", 1, 0, 1)) ? sched : nullptr;
+      if (rc.pair) return launch_f8<256, true, true>(ma, ma32, mb, p, row_scale, grid, stream);
+      if (rc.block_n == 256) return launch_f8<256, false, true>(ma, ma32, mb, p, row_scale, grid, stream);
+      return launch_f8<128, false, true>(ma, ma32, mb, p, row_scale, grid, stream);
+    }
     // Rows up to 8192 elements are split from registers (read once, all loads in flight);
     // longer ones by the two-pass kernel.
     if (k <= 2048)
@@ -704,7 +736,7 @@ size_t tkmx_ragged_dot_workspace_bytes(int op, int64_t m, int64_t k, int64_t n, 
   (void)n; (void)g; (void)config;
   // Only the forward with e4m3 weights uses scratch: the two e4m3 planes of the split
   // activations and their row scales.  Without it the call takes the converter kernel.
-  if (op == 0 && rhs_dtype == TKMX_F8E4M3 && m > 0 && k > 0 && k % 16 == 0)
+  if (op == 0 && (rhs_dtype == TKMX_F8E4M3 || rhs_dtype == TKMX_S8) && m > 0 && k > 0 && k % 16 == 0)
     return tkmx::f8_workspace(m, k).total;
   return 0;
 }
@@ -740,7 +772,7 @@ int tkmx_ragged_dot_fwd(const void* lhs, const void* rhs, const int32_t* group_s
 int tkmx_ragged_dot_fwd_gateup(const void* lhs, const void* rhs, const int32_t* group_sizes, void* out,
                                int64_t m, int64_t k, int64_t n, int64_t g, int in_dtype, int out_dtype,
                                int activation, const tkmx_config* config, void* cuda_stream) {
-  if (activation <= 0) return TKMX_ERR_INVALID_ARGUMENT;
+  if (activation <= 0 || activation > tkmx::kGateUpSiluClamp) return TKMX_ERR_INVALID_ARGUMENT;
   return run_rows(lhs, rhs, true, group_sizes, nullptr, out, m, k, n, g, g, in_dtype, in_dtype, out_dtype,
                   config, static_cast<cudaStream_t>(cuda_stream), true, 0, -1, activation);
 }
@@ -1216,6 +1248,7 @@ int tkmx_ep_moe_fused(const void* tokens, const int32_t* sorted_pair, const void
   p.tma_store = 0;
   assign_sched(*dev, &p, true);
   p.swap_rows = rc.pair ? env_int("TKMX_SWAP_ROWS", 192, 0, 192) : 0;
+  p.balance_tiles = env_int("TKMX_BALANCE_TILES", 0, 0, 1);
 
   tkmx::EpFusedParams ep = {};
   ep.tokens = tokens;

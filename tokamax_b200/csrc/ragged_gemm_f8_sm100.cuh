@@ -218,6 +218,73 @@ split_rows_e4m3_regs_kernel(const __nv_bfloat16* __restrict__ lhs, uint8_t* __re
   }
 }
 
+// int8 form of the split (weights stored as int8, multiplied by kind::i8 MMAs): the row scale
+// is s = max|a| / 127, hi = rne(a / s), lo = rne((a / s - hi) * 254), so that
+// a = s * (hi + lo / 254) to ~15 bits; both planes are int8 in [-127, 127].  One warp per row,
+// kVecs 16-byte pieces per lane and pass; rows that fit one pass are read once.
+constexpr float kS8LoSteps = 254.0f;
+template <int kVecs>
+__global__ void __launch_bounds__(256)
+split_rows_s8_kernel(const __nv_bfloat16* __restrict__ lhs, uint8_t* __restrict__ hi,
+                     uint8_t* __restrict__ lo, float* __restrict__ row_scale,
+                     int32_t* __restrict__ sched, int m, int k) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) *sched = 0;  // tile counter of the GEMM that follows
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int vecs = k / 8;
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < m; row += warps) {
+    const uint4* src = reinterpret_cast<const uint4*>(lhs + static_cast<size_t>(row) * k);
+    float amax = 0.f;
+    uint4 v[kVecs];
+    for (int base = 0; base * 32 < vecs; base += kVecs) {
+#pragma unroll
+      for (int i = 0; i < kVecs; ++i) {
+        const int at = (base + i) * 32 + lane;
+        v[i] = at < vecs ? __ldg(src + at) : make_uint4(0u, 0u, 0u, 0u);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+      }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    const float s = amax > 0.f ? fmaxf(amax * (1.0f / 127.0f), 1e-30f) : 1.0f;
+    const float inv = 1.0f / s;
+    if (lane == 0) row_scale[row] = s;
+    uint2* dhi = reinterpret_cast<uint2*>(hi + static_cast<size_t>(row) * k);
+    uint2* dlo = reinterpret_cast<uint2*>(lo + static_cast<size_t>(row) * k);
+    const bool single_pass = vecs <= kVecs * 32;   // the row is still in registers
+    for (int base = 0; base * 32 < vecs; base += kVecs) {
+#pragma unroll
+      for (int i = 0; i < kVecs; ++i) {
+        const int at = (base + i) * 32 + lane;
+        if (at >= vecs) continue;
+        const uint4 x = single_pass ? v[i] : __ldg(src + at);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+        uint32_t ph[2] = {0u, 0u}, pl[2] = {0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          const float q[2] = {f.x * inv, f.y * inv};
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int ih = max(-127, min(127, static_cast<int>(rintf(q[e]))));
+            const int il = max(-127, min(127, static_cast<int>(rintf((q[e] - static_cast<float>(ih)) * kS8LoSteps))));
+            const int byte = (2 * j + e) & 3, word = (2 * j + e) >> 2;
+            ph[word] |= (static_cast<uint32_t>(ih) & 0xFFu) << (8 * byte);
+            pl[word] |= (static_cast<uint32_t>(il) & 0xFFu) << (8 * byte);
+          }
+        }
+        dhi[at] = make_uint2(ph[0], ph[1]);
+        dlo[at] = make_uint2(pl[0], pl[1]);
+      }
+    }
+  }
+}
+
 // Workspace carve-up shared by host and device code.
 struct F8Workspace {
   size_t plane_bytes;  // one e4m3 plane, padded to 256 B
@@ -277,12 +344,26 @@ split_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ lhs, uint8_t* __restric
 // map_a8: e4m3 planes as a 3-D tensor {K, M, 2}, box {128, 128, 1}; map_a32: the same tensor
 // with 32-row boxes (short tiles).
 // map_b8: weights {N, K, G}, box {128, 64, 1}.
-template <int kBlockN, bool kPair>
+// kInt8: the same kernel for int8 weights and int8 activation planes (kind::i8, int32
+// accumulation).  The hi and lo products cannot share an integer accumulator (they carry
+// different weights, 1 and 1/254), so a full tile keeps two accumulators of kBlockN columns --
+// all of tensor memory at kBlockN = 256, hence no second buffer: the epilogue of a tile does not
+// overlap the next tile's MMAs -- and the epilogue combines them in float.
+template <int kBlockN, bool kPair, bool kInt8 = false>
 __global__ void __launch_bounds__(kF8Threads, 1)
 ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_constant__ CUtensorMap map_a32,
                       const __grid_constant__ CUtensorMap map_b8, const RaggedGemmParams p,
                       const float* __restrict__ row_scale) {
   static_assert(kBlockN == 128 || kBlockN == 256, "unsupported BLOCK_N");
+  constexpr uint32_t kAccBufs = kInt8 ? 1u : 2u;           // accumulator buffers of a tile in tensor memory
+  constexpr float kLoWeight = kInt8 ? 1.0f / kS8LoSteps : 1.0f;   // weight of the lo product against the hi one
+  auto acc_value = [](uint32_t bits) {
+    return kInt8 ? static_cast<float>(static_cast<int32_t>(bits)) : __uint_as_float(bits);
+  };
+  auto issue_mma = [](uint32_t d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    if constexpr (kInt8) ptx::umma_i8<kPair ? 2 : 1>(d, da, db, idesc, acc);
+    else ptx::umma_f8<kPair ? 2 : 1>(d, da, db, idesc, acc);
+  };
   constexpr int kCtas = kPair ? 2 : 1;
   constexpr int kTileM = kBlockM * kCtas;
   constexpr int kLocalN = kBlockN / kCtas;
@@ -537,8 +618,8 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
           break;
         }
         if (t.num_kb == 0) continue;
-        const uint32_t b = acc_cnt & 1u;
-        const uint32_t acc_ph = (acc_cnt >> 1) & 1u;
+        const uint32_t b = acc_cnt % kAccBufs;
+        const uint32_t acc_ph = (acc_cnt / kAccBufs) & 1u;
         ++acc_cnt;
         if (!bounded_wait<kPair>(bar_acc_empty + 8u * b, acc_ph ^ 1u, abort_flag, p.status, kDevTimeoutMma)) {
           ok = false;
@@ -546,6 +627,7 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
         }
         ptx::tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + b * kBlockN;
+        const uint32_t tmem_d_lo = kInt8 ? tmem_d + kBlockN : tmem_d;   // the lo product's accumulator
         const int valid = tile_valid(t);
         const bool swapped = valid <= swap_rows;
         // Swapped: per 128-column chunk of the weights D[128 output columns x (hi rows | lo rows)];
@@ -554,7 +636,8 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
         // small-N MMA costs about the same whatever N is (its time goes into fetching the
         // 128-row M operand); the epilogue adds the two halves.
         const uint32_t stacked_n = static_cast<uint32_t>(((valid + 31) >> 5) * 64);
-        const uint32_t idesc_swapped = ptx::make_idesc(0u, 0u, 1u, 0u, 128u, stacked_n);
+        const uint32_t idesc_swapped = kInt8 ? ptx::make_idesc_s8(1u, 0u, 128u, stacked_n)
+                                             : ptx::make_idesc(0u, 0u, 1u, 0u, 128u, stacked_n);
         for (int kb = 0; kb < num_kb; ++kb, pos.advance(num_stages)) {
           const uint32_t s = pos.slot;
           if (!bounded_wait<kPair>(bar_full + 8u * s, pos.phase, abort_flag, p.status, kDevTimeoutMma)) {
@@ -575,16 +658,15 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
 #pragma unroll
               for (int h = 0; h < kNChunks; ++h) {
                 const uint64_t dwk = db + ((h * kBChunkBytes + k * 4096u) >> 4);
-                ptx::umma_f8<kCtas>(tmem_d + h * 128, dwk, da_hi + ((k * 32u) >> 4), idesc_swapped,
-                                    (kb | k) != 0 ? 1u : 0u);
+                issue_mma(tmem_d + h * 128, dwk, da_hi + ((k * 32u) >> 4), idesc_swapped, (kb | k) != 0 ? 1u : 0u);
               }
             }
           } else {
 #pragma unroll
             for (int k = 0; k < kF8BlockK / 32; ++k) {
               const uint64_t dbk = db + ((k * 4096u) >> 4);
-              ptx::umma_f8<kCtas>(tmem_d, da_hi + ((k * 32u) >> 4), dbk, p.idesc, (kb | k) != 0 ? 1u : 0u);
-              ptx::umma_f8<kCtas>(tmem_d, da_lo + ((k * 32u) >> 4), dbk, p.idesc, 1u);
+              issue_mma(tmem_d, da_hi + ((k * 32u) >> 4), dbk, p.idesc, (kb | k) != 0 ? 1u : 0u);
+              issue_mma(tmem_d_lo, da_lo + ((k * 32u) >> 4), dbk, p.idesc, (kInt8 && (kb | k) == 0) ? 0u : 1u);
             }
           }
           if constexpr (kPair) ptx::umma_commit_pair(bar_empty + 8u * s, 3);
@@ -639,8 +721,8 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
       uint32_t b = 0;
       const bool has_acc = t.num_kb > 0;
       if (has_acc) {
-        b = acc_cnt & 1u;
-        const uint32_t acc_ph = (acc_cnt >> 1) & 1u;
+        b = acc_cnt % kAccBufs;
+        const uint32_t acc_ph = (acc_cnt / kAccBufs) & 1u;
         ++acc_cnt;
         if (!bounded_wait<kPair>(bar_acc_full + 8u * b, acc_ph, abort_flag, p.status, kDevTimeoutEpilogue)) {
           ok = false;
@@ -677,7 +759,7 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
             const float my_rs = my_r < valid ? __ldg(row_scale + t.row0 + my_r) : 0.f;
             ptx::tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) vg[i] = __float_as_uint(__uint_as_float(va[i]) + __uint_as_float(vb[i]));
+            for (int i = 0; i < 32; ++i) vg[i] = __float_as_uint(acc_value(va[i]) + kLoWeight * acc_value(vb[i]));
             ptx::tmem_ld_32x32b_x32(tmem_row + 128 + rc * 32, va);
             ptx::tmem_ld_32x32b_x32(tmem_row + 128 + (row_chunks + rc) * 32, vb);
             ptx::tmem_wait_ld();
@@ -687,7 +769,7 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
               const int r = rc * 32 + i;
               if (r < valid && n_ok) {
                 const float g = __uint_as_float(vg[i]) * rsi * cs_g + bs_g;
-                const float u = (__uint_as_float(va[i]) + __uint_as_float(vb[i])) * rsi * cs_u + bs_u;
+                const float u = (acc_value(va[i]) + kLoWeight * acc_value(vb[i])) * rsi * cs_u + bs_u;
                 store_one(gateup_act(p.gateup, g, u), r, n);
               }
             }
@@ -711,7 +793,7 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
                 const float rsi = __shfl_sync(0xffffffffu, my_rs, i);
                 const int r = rc * 32 + i;
                 if (r < valid && n_ok)
-                  store_one((__uint_as_float(va[i]) + __uint_as_float(vb[i])) * rsi * cs + bs, r, n);
+                  store_one((acc_value(va[i]) + kLoWeight * acc_value(vb[i])) * rsi * cs + bs, r, n);
               }
             }
           }
@@ -773,6 +855,23 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
         }
         store_chunk(p, v, nullptr, row_ok, out_row_off, t.col0 + c * 32, p.cols);
       };
+      if constexpr (kInt8) {
+        // hi product in accumulator columns [0, kBlockN), lo product kBlockN columns further.
+#pragma unroll 1
+        for (int c = 0; c < n_chunks; ++c) {
+          if (has_acc) {
+            if (c > 0) ptx::tmem_ld_32x32b_x32(tmem_row + c * 32, va);
+            ptx::tmem_ld_32x32b_x32(tmem_row + kBlockN + c * 32, vb);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) va[i] = __float_as_uint(acc_value(va[i]) + kLoWeight * acc_value(vb[i]));
+          } else if (c > 0) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) va[i] = 0u;
+          }
+          scaled_store(va, c);
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < n_chunks; c += 2) {
         if (has_acc) {
@@ -787,6 +886,7 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
           }
           scaled_store(vb, c + 1);
         }
+      }
       }
       }
       if (has_acc) {

@@ -94,6 +94,7 @@ struct RaggedGemmParams {
   int32_t minor_is_m;          // 1: row tiles vary fastest inside a band, 0: column tiles
   int32_t num_stages;          // smem ring depth
   int32_t gateup;              // kRowsBN: 0 = plain; else GateUpAct: out[:, j] = act(acc[:, j]) * acc[:, cols/2 + j]
+  int32_t activation;          // rows modes: ElementAct applied to the float32 result (after scale and bias), 0 = none
   int32_t prefetch_blocks;     // fp8 kernel: weight blocks requested into L2 ahead of the smem ring (0: none)
   unsigned long long* sched_slot;  // 16-bit kernels: (epoch << 32 | next tile) word for dynamic scheduling, or null;
                                    //   the word after it counts the units that have finished drawing
@@ -101,6 +102,7 @@ struct RaggedGemmParams {
   int32_t* sched_counter;      // fp8 kernel: zeroed tile counter for dynamic scheduling, or null (static)
   int32_t mixed_order;         // fp8 kernel visiting order: 0 = by index, 1 = small and large groups merged, 2 = large groups first
   int32_t swap_rows;           // tiles with at most this many rows swap the MMA operands (0: never); see kernels
+  int32_t balance_tiles;       // 1: cut multi-tile groups into equal swapped tiles where possible (see TileWalker)
   int32_t* status;             // device status word (see DeviceStatus)
 };
 
@@ -108,6 +110,8 @@ constexpr int kBlockM = 128;        // UMMA M (token rows, or lhs features in co
 constexpr int kBlockK = 64;         // contraction elements per ring stage (one 128 B swizzle row)
 constexpr int kUmmaK = 16;          // contraction elements per tcgen05.mma (16-bit inputs)
 constexpr int kNumThreads = 256;
+constexpr int kEpNumThreads = 384;  // expert-parallel form: four more warps that only send rows
+constexpr int kEpSendWarps = 6;     // warps 2, 3 and 8-11
 constexpr int kATileBytes = kBlockM * kBlockK * 2;  // 16 KiB
 constexpr int kChunkBytes = 64 * 128;               // one [64 x 128 B] TMA box
 constexpr int kStagingBytes = 32 * 128;             // one epilogue warp's [32 rows x 64 bf16] block
@@ -256,7 +260,7 @@ struct RingPos {
 struct Tile {
   int group;     // group index, or -1 for a zero-fill tile (rows past sum(group_sizes))
   int row0;      // first output row of the tile (rows modes: token row; contract: feature row)
-  int row_end;   // one past the last valid output row of the tile's group / matrix
+  int row_end;   // one past the last output row the tile owns (its group's or the matrix's end at most)
   int col0;      // first output column
   int c_begin;   // contract mode: first token row of the group
   int c_end;     // contract mode: one past the last token row of the group
@@ -340,6 +344,11 @@ struct TileWalker {
   int cursor;  // rows modes: current position in the visiting order
   int cycles, rhs_groups;
   const int* order = nullptr;  // rows modes: explicit visiting order (smem), or null for the cyclic rule
+  // Rows modes with swapped short tiles (pair mode): a group that needs several row tiles is cut
+  // into EQUAL tiles (rounded up to 16 rows) when those are short enough to run swapped, since
+  // a swapped tile's MMA time follows its rows while a full tile costs the same however few of
+  // its rows are valid: 272 rows are two tiles of 144 instead of 256 + 16.
+  int balance_rows = 0;
 
   __device__ TileWalker(const RaggedGemmParams& p, const int* rs, const int* ts, int unit,
                         int num_units)
@@ -367,6 +376,7 @@ struct TileWalker {
     cursor = 0;
     rhs_groups = p.rhs_groups;
     cycles = visit_cycles(p.num_groups, p.rhs_groups);
+    if (kMode != kContract && kTileM == 2 * kBlockM && kBlockN == 256 && p.balance_tiles) balance_rows = p.swap_rows;
   }
 
   // Band rasterisation: the minor dimension is cut into bands `tile_width` wide; inside
@@ -428,9 +438,15 @@ struct TileWalker {
       int mi, ni;
       if (minor_is_m) raster(local, m_tiles, n_tiles, mi, ni);
       else raster(local, n_tiles, m_tiles, ni, mi);
+      int tile_rows = kTileM;
+      if (balance_rows > 0 && m_tiles > 1) {
+        const int rows_g = row_start[g + 1] - row_start[g];
+        const int even = ((rows_g + m_tiles - 1) / m_tiles + 15) & ~15;
+        if (even <= balance_rows && (m_tiles - 1) * even < rows_g) tile_rows = even;
+      }
       t.group = g;
-      t.row0 = row_start[g] + mi * kTileM;
-      t.row_end = row_start[g + 1];
+      t.row0 = row_start[g] + mi * tile_rows;
+      t.row_end = min(t.row0 + tile_rows, row_start[g + 1]);   // the tile's own end
       t.col0 = ni * kBlockN;
       t.c_begin = t.c_end = 0;
       t.num_kb = (cdim + kBlockK - 1) / kBlockK;
@@ -459,6 +475,31 @@ enum GateUpAct : int {
   kGateUpSwigluOai = 3,
   kGateUpSiluClamp = 4,
 };
+
+// Elementwise activations fused on the float32 accumulator (`activation=` of ragged_dot,
+// tokamax/_src/ops/ragged_dot/api.py:108-113: applied in the accumulator's dtype before the
+// cast to the output dtype).
+enum ElementAct : int {
+  kActNone = 0,
+  kActRelu = 1,
+  kActSilu = 2,
+  kActGeluTanh = 3,
+  kActGeluErf = 4,
+  kActTanh = 5,
+  kActSigmoid = 6,
+};
+
+__device__ __forceinline__ float element_act(int kind, float x) {
+  switch (kind) {
+    case kActRelu: return fmaxf(x, 0.f);
+    case kActSilu: return x / (1.f + expf(-x));
+    case kActGeluTanh: return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    case kActGeluErf: return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+    case kActTanh: return tanhf(x);
+    case kActSigmoid: return 1.f / (1.f + expf(-x));
+  }
+  return x;
+}
 
 __device__ __forceinline__ float gateup_act(int kind, float g, float u) {
   switch (kind) {
@@ -502,6 +543,10 @@ __device__ __forceinline__ void store_chunk(const RaggedGemmParams& p, uint32_t 
       v[i] = __float_as_uint(__uint_as_float(v[i]) + b);
     }
   }
+  if (p.activation != 0) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(element_act(p.activation, __uint_as_float(v[i])));
+  }
   if (!row_ok) return;
   if (p.out_is_f32) {
     float* dst = reinterpret_cast<float*>(p.out) + out_row_off + col;
@@ -542,7 +587,7 @@ __device__ __forceinline__ void store_chunk(const RaggedGemmParams& p, uint32_t 
 // warps multiply what has arrived (the producer waits on per-expert arrival counters), and the
 // epilogue stores finished rows straight into the source ranks' return buffers (`p.out` unused).
 template <int kMode, int kBlockN, bool kPair, bool kEp = false>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(kEp ? kEpNumThreads : kNumThreads, 1)
 ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_out, const RaggedGemmParams p,
                    const __grid_constant__ EpFusedParams ep) {
@@ -684,7 +729,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   if (warp == 3) scan_groups<kTileM, kMode != kContract>(p, row_start, tile_start, lane);
   if constexpr (kEp) {
     const EpPlanLayout pl = ep_plan_layout(ep.num_experts, ep.world);
-    for (int i = threadIdx.x; i <= ep.num_experts; i += kNumThreads) ep_vstart[i] = __ldg(ep.plan + pl.vstart + i);
+    for (int i = threadIdx.x; i <= ep.num_experts; i += kEpNumThreads) ep_vstart[i] = __ldg(ep.plan + pl.vstart + i);
   }
   ptx::tcgen05_fence_before();
   __syncthreads();
@@ -951,12 +996,14 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
       }
     }
-  } else if (warp == 2 || warp == 3) {
+  } else if (warp == 2 || warp == 3 || warp >= 8) {
     if constexpr (kEp) {
-      // ===== expert-parallel senders: two warps per CTA, all CTAs of the grid =====
+      // ===== expert-parallel senders: six warps per CTA (2, 3, 8-11), all CTAs of the grid.
+      // Consecutive items go to different CTAs, so every SM's links carry every expert. =====
+      const int local = warp < 8 ? warp - 2 : warp - 6;
       if (ep.phases & 1)
-        ep_send_rows(ep, ep_vstart, static_cast<int>(blockIdx.x) * 2 + (warp - 2), static_cast<int>(gridDim.x) * 2,
-                     lane, p.status);
+        ep_send_rows(ep, ep_vstart, local * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x),
+                     kEpSendWarps * static_cast<int>(gridDim.x), lane, p.status);
     }
     if (kMode == kContract && warp == 2) {
       // ===== tail fix-up: zero the rows of the last contraction block that lie past
@@ -1009,7 +1056,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 4 && warp < 8) {
     // ===== epilogue: this CTA's 128 rows of the tile =====
     const int ew = warp - 4;  // == warp % 4: the TMEM lane quarter this warp may read
     Walker walk(p, row_start, tile_start, unit, num_units);
@@ -1102,7 +1149,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             if (rc * 32 + i < valid && n_ok) {
-              const float val = __uint_as_float(v[i]) * cs + bs;
+              const float val = element_act(p.activation, __uint_as_float(v[i]) * cs + bs);
               const size_t off = off0 + static_cast<size_t>(i) * ld_out;
               if (p.out_is_f32) reinterpret_cast<float*>(p.out)[off] = val;
               else if (p.out_is_f16) reinterpret_cast<__half*>(p.out)[off] = __float2half_rn(val);
@@ -1177,7 +1224,13 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll 1
       for (int c = 0; c < n_chunks; ++c) {
         const int col = t.col0 + c * 64;
-        if (has_acc) ptx::tmem_wait_ld();
+        if (has_acc) {
+          ptx::tmem_wait_ld();
+        } else if (c > 0 && p.activation != 0) {
+          // zero-fill tile: the previous chunk's activation was applied in place
+#pragma unroll
+          for (int i = 0; i < 32; ++i) va[i] = vb[i] = 0u;
+        }
         if constexpr (kEp) {
           // 32 rows x 64 columns through the swizzled staging block, then out by rows: eight
           // lanes write one row's 128 contiguous bytes into its source rank's return buffer.
@@ -1214,6 +1267,13 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
         if (use_tma) {
           uint32_t w[32];
+          if (p.activation != 0) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              va[i] = __float_as_uint(element_act(p.activation, __uint_as_float(va[i])));
+              vb[i] = __float_as_uint(element_act(p.activation, __uint_as_float(vb[i])));
+            }
+          }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             w[i] = p.out_is_f16 ? pack_f16x2(__uint_as_float(va[2 * i]), __uint_as_float(va[2 * i + 1]))
@@ -1264,7 +1324,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   }
 
   // Outstanding TMA stores read this CTA's shared memory: let them finish before it retires.
-  if (warp >= 4 && lane == 0) ptx::bulk_wait_group0();
+  if (warp >= 4 && warp < 8 && lane == 0) ptx::bulk_wait_group0();
 
   // ------------------------------------------------------------------ teardown
   ptx::tcgen05_fence_before();

@@ -109,6 +109,39 @@ def canonicalize_precision(precision):
   return name
 
 
+def fusable_activation(activation) -> str | None:
+  """Name of the epilogue activation that computes `activation`, or None if the callable is not
+  one of the recognised ones (it is then applied after the kernel, like upstream does for
+  backends without fusion).  Recognised: the torch / torch.nn.functional functions and module
+  instances for relu, silu, gelu (erf form, or approximate="tanh"), tanh and sigmoid, and the
+  same names as strings."""
+  import functools
+  import torch.nn.functional as F
+  if activation is None:
+    return None
+  if isinstance(activation, str):
+    return activation if activation in _capi.ELEMENT_ACTIVATIONS else None
+  table = {torch.relu: "relu", F.relu: "relu", F.silu: "silu", torch.tanh: "tanh", F.tanh: "tanh",
+           torch.sigmoid: "sigmoid", F.sigmoid: "sigmoid", F.gelu: "gelu_erf"}
+  try:
+    if activation in table:
+      return table[activation]
+  except TypeError:
+    pass
+  if isinstance(activation, functools.partial) and activation.func is F.gelu and not activation.args:
+    kw = dict(activation.keywords)
+    approx = kw.pop("approximate", "none")
+    if not kw and approx in ("none", "tanh"):
+      return "gelu_tanh" if approx == "tanh" else "gelu_erf"
+  if isinstance(activation, torch.nn.GELU):
+    return "gelu_tanh" if activation.approximate == "tanh" else "gelu_erf"
+  for cls, name in ((torch.nn.ReLU, "relu"), (torch.nn.SiLU, "silu"), (torch.nn.Tanh, "tanh"),
+                    (torch.nn.Sigmoid, "sigmoid")):
+    if type(activation) is cls:
+      return name
+  return None
+
+
 def _as_int32_device(gs, device) -> torch.Tensor:
   if isinstance(gs, GroupSizes):
     gs = gs.value
@@ -229,7 +262,17 @@ class B200RaggedDot(base.RaggedDot):
     if dims == base.DEFAULT_RAGGED_DOT_DIM_NUMS:
       if lhs.ndim != 2 or rhs.ndim != 3 or lhs.shape[1] != rhs.shape[1]:
         raise ValueError(f"incompatible shapes {tuple(lhs.shape)} and {tuple(rhs.shape)}")
-      if fuse_gateup_activation is not None or bias is not None:
+      # `activation` on the float32 accumulator inside the kernel (api.py:108-113 upstream), for
+      # the callables the epilogue knows; never when the residuals (the result before the
+      # activation) are asked for, and only on the plain 16-bit forward.
+      fused_act = None
+      if (activation is not None and not return_residuals and scale is None and not windowed
+          and fuse_gateup_activation is None and lhs.dtype == rhs.dtype
+          and (lhs.shape[0] == 0 or rhs.shape[0] > 0)):
+        fused_act = fusable_activation(activation)
+        if fused_act == "sigmoid" and (rhs.shape[0] == 0 or lhs.shape[1] == 0):
+          fused_act = None
+      if fuse_gateup_activation is not None or bias is not None or fused_act is not None:
         # Fused epilogue: tmp = ragged_dot(lhs, rhs) [* scale] + bias[group]; with
         # fuse_gateup_activation rhs = [gate | up] and out = act(tmp[:, :n/2]) * tmp[:, n/2:], so
         # the full-width product never reaches HBM (base.py:207-217 upstream).
@@ -258,9 +301,10 @@ class B200RaggedDot(base.RaggedDot):
         out_cols = n // 2 if fuse_gateup_activation is not None else n
         out = torch.empty((lhs.shape[0], out_cols), dtype=out_dtype, device=lhs.device)
         _capi.ragged_dot_fwd_epilogue(lhs, rhs, gs, out, rhs_scale=scale, rhs_bias=bias,
-                                      activation=fuse_gateup_activation, config=ccfg, workspace=workspace)
+                                      activation=fuse_gateup_activation, element_activation=fused_act,
+                                      config=ccfg, workspace=workspace)
         residuals = out   # with the bias, before `activation`; never requested with gate/up
-        if activation is not None:
+        if activation is not None and fused_act is None:
           out = activation(out)
         return out, residuals if return_residuals else None
       out = torch.empty((lhs.shape[0], rhs.shape[2]), dtype=out_dtype, device=lhs.device)
@@ -367,9 +411,12 @@ class B200RaggedDot(base.RaggedDot):
     number of 128-byte swizzle rows for both operands; num_stages {2, 4};
     grid_minor_dim {M, N}; grid_tile_width {1, 2, 4, 8}; split_m {1}; collective
     {True, False}; post_scale {False} (prefill) / {True, False} (generate).
-    `collective=True` and `post_scale=True` entries are listed (they are part of the
-    space) but refused by `_fwd` until those kernels exist; the autotuner records the
-    refusal like any other failed config (autotuner.py:173-203 upstream).
+    `collective=True` entries run the CTA-pair kernel.  `post_scale=True` entries are listed
+    (they are part of the space) but refused by `Config.to_capi`; the autotuner records the
+    refusal like any other failed config (autotuner.py:173-203 upstream).  `block_m` below 128
+    has no kernel of its own (the UMMA shape is 128 or 256 rows; few-row tiles are handled by
+    the swapped-operand path inside the kernels), so those entries run like block_m = 128 and
+    the autotuner, which keys on `Config.native()`, times each distinct kernel once.
     """
     lhs, rhs = ba.args[:2]
     bits = lambda dt: torch.finfo(dt).bits if dt.is_floating_point else torch.iinfo(dt).bits
