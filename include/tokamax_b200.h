@@ -187,6 +187,18 @@ TKMX_API int tkmx_ragged_dot_drhs(const void* lhs, const void* dout, const int32
                          const tkmx_config* config, void* cuda_stream);
 
 /*
+ * tkmx_ragged_dot_drhs for an expert-parallel shard: group_sizes counts all g groups of the
+ * global problem, but only the groups [group_begin, group_begin + group_count) are contracted,
+ * into drhs [group_count, k, n] (slab j = group group_begin + j).  The `num_actual_groups` /
+ * `group_offset` pair of the reference's tgmm (tokamax/_src/ops/ragged_dot/pallas_mosaic_tpu_v2.py:89-93,
+ * arithmetic of reference_tgmm, tokamax/_src/ops/experimental/gmm_v2/gmm_v2_test.py:109-160).
+ */
+TKMX_API int tkmx_ragged_dot_drhs_window(const void* lhs, const void* dout, const int32_t* group_sizes,
+                                         void* drhs, int64_t m, int64_t k, int64_t n, int64_t g,
+                                         int64_t group_begin, int64_t group_count, int in_dtype,
+                                         int out_dtype, const tkmx_config* config, void* cuda_stream);
+
+/*
  * Group bookkeeping as its own kernel, for callers (and tests) that need the arrays:
  * the tile table the reference computes with XLA ops before its kernel
  * (GroupInfo.create_aligned, pallas_mosaic_gpu_common.py:88-151).  All outputs are

@@ -284,3 +284,47 @@ def test_epilogue_keyword_validation_needs_no_gpu():
     op(lhs, rhs, group_sizes=gs, rhs_bias=torch.zeros(2, 1, 32), fuse_gateup_activation="silu")
   with pytest.raises(NotImplementedError):   # still refused, like the reference's GPU backends
     op(lhs, rhs, group_sizes=gs, maybe_quantize_lhs=True)
+
+
+def test_cache_wire_format_is_the_references():
+  """Keys and configs are written in the wire format of the reference's cache files
+  (tokamax/_src/autotuning/cache.py:81-110; example keys below are of the form found in
+  tokamax/data/autotuning/nvidia_b200/pallas_mosaic_gpu_ragged_dot.json): such a key parses,
+  binds, and serialises back to the identical string; a config with the older `async_store`
+  field parses; a caller's tensors hit the entry loaded from the file."""
+  op = b200.B200RaggedDot()
+  keys = [
+      '{"lhs":"bf16[262144,7168]","rhs":"bf16[256,7168,2048]","group_sizes":{"num_groups":256,"total_size":262144},'
+      '"ragged_dot_dimension_numbers":{"dot_dimension_numbers":[[[1],[1]],[[],[]]],"lhs_ragged_dimensions":[0],'
+      '"rhs_group_dimensions":[0]},"precision":["DEFAULT","DEFAULT"],"preferred_element_type":null,'
+      '"return_residuals":false,"activation":null}',
+      '{"lhs":"bf16[131072,2048]","rhs":"bf16[131072,768]","group_sizes":{"num_groups":128,"total_size":131072},'
+      '"ragged_dot_dimension_numbers":{"dot_dimension_numbers":[[[0],[0]],[[],[]]],"lhs_ragged_dimensions":[0],'
+      '"rhs_group_dimensions":[]},"precision":["DEFAULT","DEFAULT"],"preferred_element_type":null,'
+      '"return_residuals":false,"activation":null}',
+      '{"lhs":"bf16[8,4096]","rhs":"bf16[8,4096,4096]","group_sizes":[1,1,1,1,1,1,1,1],'
+      '"ragged_dot_dimension_numbers":{"dot_dimension_numbers":[[[1],[1]],[[],[]]],"lhs_ragged_dimensions":[0],'
+      '"rhs_group_dimensions":[0]},"precision":["DEFAULT","DEFAULT"],"preferred_element_type":null,'
+      '"return_residuals":false,"activation":null}',
+  ]
+  for key in keys:
+    ba = op.bind(**cache.spec_from_json(key))
+    assert cache.spec_to_json(dict(ba.arguments)) == key
+  cfg_json = ('{"block_m":128,"block_n":128,"block_k":128,"num_stages":2,"split_k":1,"split_m":1,"persistent":false,'
+              '"async_store":false,"post_scale":false,"collective":true,"grid_minor_dim":0,"grid_tile_width":2}')
+  cfg = cache.config_from_json(b200.Config, cfg_json)
+  assert cfg.collective and cfg.grid_tile_width == 2 and cfg.block_k == 128
+  assert cache.config_to_json(cfg) == cfg_json
+  # a call with plain tensors (bare group_sizes array) finds the entry a file key binds to
+  ba_file = op.bind(**cache.spec_from_json(keys[0]))
+  lhs = torch.empty(262144, 7168, dtype=torch.bfloat16, device="meta")
+  rhs = torch.empty(256, 7168, 2048, dtype=torch.bfloat16, device="meta")
+  gs = torch.empty(256, dtype=torch.int32, device="meta")
+  assert op.bind(lhs, rhs, group_sizes=gs).autotuning_cache_key == ba_file.autotuning_cache_key
+  ba_drhs = op.bind(**cache.spec_from_json(keys[1]))
+  a = torch.empty(131072, 2048, dtype=torch.bfloat16, device="meta")
+  d = torch.empty(131072, 768, dtype=torch.bfloat16, device="meta")
+  g2 = torch.empty(128, dtype=torch.int32, device="meta")
+  from tokamax_b200.ragged_dot import base as base_lib
+  assert op.bind(a, d, group_sizes=g2, ragged_dot_dimension_numbers=base_lib.RAGGED_CONTRACTING_DOT_DIM_NUMS
+                 ).autotuning_cache_key == ba_drhs.autotuning_cache_key

@@ -1220,3 +1220,52 @@ def test_two_launches_on_one_tile_counter_word_report_a_conflict(capi, monkeypat
   capi.device_status()                                           # the device keeps working
   if not conflict:     # the launches happened not to overlap: then both results must be complete
     assert torch.equal(outs[0], want) and torch.equal(outs[1], want)
+
+
+# ---------------------------------------------------------------- expert-parallel affordances of drhs
+@pytest.mark.parametrize("collective", [0, 1])
+def test_drhs_group_window_num_actual_groups(capi, collective):
+  """`num_actual_groups` + `group_offset` of the drhs (tgmm) call: global group_sizes, only the
+  local experts' slabs are produced (reference_tgmm, gmm_v2_test.py:109-160)."""
+  from tokamax_b200.ragged_dot import b200 as b200_lib
+  from tokamax_b200.ragged_dot import base as base_lib
+  g, m, k, n = 8, 1100, 256, 320
+  lhs, _, dout, rng = helpers.seeded_inputs("drhs-window", m, k, n, g)
+  gs = np.array([100, 0, 257, 64, 300, 129, 0, 200], np.int32)      # 50 rows of no group
+  want = ref.ragged_dot_ref(lhs, dout, gs, dims=ref.RAGGED_CONTRACTING, out_dtype=torch.float32)
+  for begin, count in ((0, 8), (2, 4), (5, 3), (3, 0), (7, 1)):
+    out = torch.full((count, k, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    capi.ragged_dot_drhs(lhs.cuda(), dout.cuda(), _gs_dev(gs), out, group_begin=begin,
+                         config=capi.Config(block_n=256, collective=collective))
+    capi.device_status()
+    if count:
+      helpers.assert_close(out, want[begin:begin + count], what=f"drhs window [{begin}, {begin + count})")
+  op = b200_lib.B200RaggedDot(num_actual_groups=4)
+  out = op(lhs.cuda(), dout.cuda(), group_sizes=_gs_dev(gs), group_offset=torch.tensor([2]),
+           ragged_dot_dimension_numbers=base_lib.RAGGED_CONTRACTING_DOT_DIM_NUMS)
+  assert tuple(out.shape) == (4, k, n)
+  helpers.assert_close(out, want[2:6], what="num_actual_groups through the op")
+  with pytest.raises(ValueError):
+    op(lhs.cuda(), dout.cuda(), group_sizes=_gs_dev(gs), group_offset=torch.tensor([6]),
+       ragged_dot_dimension_numbers=base_lib.RAGGED_CONTRACTING_DOT_DIM_NUMS)
+
+
+def test_as_qarray_and_vjp_with_quantised_rhs(tk, capi):
+  """AsQArray is quantised next to the kernel call (tokamax/_src/quantization.py:39-72); with a
+  quantised rhs the backward pass still gives dlhs (from the dequantised weights), as the
+  reference's vjp does (base.py:434-446)."""
+  g, m, k, n = 4, 512, 256, 384
+  lhs, w, dout, _ = helpers.seeded_inputs("asq", m, k, n, g, scale=0.3)
+  gs = np.array([100, 200, 12, 200], np.int32)
+  for qtype in (torch.float8_e4m3fn, torch.int8):
+    q, scale = ref.quantize_tensor_ref(w, qtype)
+    want = ref.ragged_dot_ref(lhs, q, gs, rhs_scale=scale, out_dtype=torch.float32)
+    out = tk.ragged_dot(lhs.cuda(), tk.AsQArray(w.cuda(), qtype), _gs_dev(gs))
+    helpers.assert_close(out, want, atol=helpers.Q_ATOL, rtol=helpers.Q_RTOL, what=f"AsQArray {qtype}")
+  qa = tk.quantize_per_channel(w.cuda(), torch.float8_e4m3fn)
+  a = lhs.cuda().requires_grad_(True)
+  out = tk.ragged_dot(a, qa, _gs_dev(gs))
+  (dl,) = torch.autograd.grad(out, (a,), dout.cuda())
+  deq = (qa.qvalue.float() * qa.scale.float()).bfloat16()
+  want_dl = ref.ragged_dot_ref(dout, deq.cpu(), gs, dims=ref.TRANS_RHS, out_dtype=torch.float32)
+  helpers.assert_close(dl, want_dl, atol=helpers.Q_ATOL, rtol=helpers.Q_RTOL, what="dlhs with quantised rhs")

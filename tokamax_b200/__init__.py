@@ -9,7 +9,7 @@ from tokamax_b200 import config
 from tokamax_b200.autotuning import AutotuningResult, autotune
 from tokamax_b200.benchmarking import BenchmarkData, benchmark, standardize_function
 from tokamax_b200.op import BoundArguments, Op
-from tokamax_b200.quantization import QArray, quantize_per_channel
+from tokamax_b200.quantization import AsQArray, QArray, quantize_per_channel
 from tokamax_b200.ragged_dot import (
     GroupSizes as RaggedDotGroupSizes,
     generate_group_sizes as generate_ragged_dot_group_sizes,
@@ -20,7 +20,7 @@ from tokamax_b200.ragged_dot import (
 )
 
 __all__ = [
-    "AutotuningResult", "BenchmarkData", "BoundArguments", "HostRaggedDot", "Op", "QArray",
+    "AsQArray", "AutotuningResult", "BenchmarkData", "BoundArguments", "HostRaggedDot", "Op", "QArray",
     "RaggedDotGroupSizes", "autotune", "benchmark", "config",
     "generate_ragged_dot_group_sizes", "quantize_per_channel", "ragged_dot",
     "ragged_dot_general", "ragged_dot_host", "standardize_function",

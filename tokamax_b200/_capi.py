@@ -63,6 +63,7 @@ EXPORTED_SYMBOLS = (
     "tkmx_ep_exchange_plan",
     "tkmx_ep_moe_fused",
     "tkmx_cross_rank_barrier",
+    "tkmx_ragged_dot_drhs_window",
 )
 
 
@@ -119,6 +120,9 @@ def load() -> ctypes.CDLL:
     for fn in (lib.tkmx_ragged_dot_dlhs, lib.tkmx_ragged_dot_drhs):
       fn.restype = ctypes.c_int
       fn.argtypes = [vp, vp, vp, vp, vp, sz, i64, i64, i64, i64, ctypes.c_int, ctypes.c_int, cfgp, vp]
+    lib.tkmx_ragged_dot_drhs_window.restype = ctypes.c_int
+    lib.tkmx_ragged_dot_drhs_window.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, ctypes.c_int,
+                                                ctypes.c_int, cfgp, vp]
     lib.tkmx_group_info_aligned.restype = ctypes.c_int
     lib.tkmx_group_info_aligned.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]
     lib.tkmx_device_status.restype = ctypes.c_int
@@ -474,11 +478,20 @@ def ragged_dot_dlhs(dout, rhs, group_sizes, dlhs, *, config: Config | None = Non
 
 
 def ragged_dot_drhs(lhs, dout, group_sizes, drhs, *, config: Config | None = None,
-                    workspace=None) -> None:
+                    workspace=None, group_begin: int | None = None) -> None:
+  """drhs[j] = lhs[rows of group j]^T @ dout[rows of group j].  With `group_begin` the output
+  holds only the groups [group_begin, group_begin + drhs.shape[0]) of the group_sizes array."""
   dev = _require_cuda(lhs, dout, group_sizes, drhs, workspace)
   m, k = lhs.shape
   n = dout.shape[1]
   g = drhs.shape[0]
+  if group_begin is not None:
+    with torch.cuda.device(dev):
+      st = load().tkmx_ragged_dot_drhs_window(
+          _ptr(lhs), _ptr(dout), _ptr(group_sizes), _ptr(drhs), m, k, n, group_sizes.numel(), group_begin, g,
+          dtype_code(lhs.dtype), dtype_code(drhs.dtype), _cfg(config), _stream(dev))
+    check(st, "tkmx_ragged_dot_drhs_window")
+    return
   with torch.cuda.device(dev):
     st = load().tkmx_ragged_dot_drhs(
         _ptr(lhs), _ptr(dout), _ptr(group_sizes), _ptr(drhs), _ptr(workspace),

@@ -2,9 +2,10 @@
 
 Same file naming as tokamax/_src/autotuning/cache.py:81-110:
 `data/autotuning/<device kind lower-cased, spaces -> '_'>/<snake_case op class>.json`,
-a JSON object mapping a serialised argument spec to `{serialised config: BenchmarkData}`.
-The argument-spec and config serialisations are this package's own
-(`spec_to_json` below), read lazily on first access per device kind.
+a JSON object mapping a serialised argument spec to `{serialised config: BenchmarkData}`,
+keys and values in the reference's wire format (`spec_to_json` / `config_to_json` below), so
+that an entry of the reference's own cache files parses here and the files written here parse
+upstream; read lazily on first access per device kind.
 """
 
 from __future__ import annotations
@@ -36,57 +37,117 @@ def cache_file(op, device_kind: str, base_dir: str = CACHE_PATH) -> str:
   return os.path.join(base_dir, kind, f"{op_name}.json")
 
 
-def _encode(v: Any) -> Any:
-  from tokamax_b200.ragged_dot.base import GroupSizes, RaggedDotDimensionNumbers
-  if isinstance(v, op_lib.ShapeDtype):
-    return v.short()
+# Field order of a key, as the reference writes it (the order of `_fwd`'s signature).
+_KEY_FIELDS = ("lhs", "rhs", "group_sizes", "ragged_dot_dimension_numbers", "precision",
+               "preferred_element_type", "return_residuals", "activation")
+# Field order of a serialised Config (tokamax/data/autotuning/nvidia_b200/pallas_mosaic_gpu_ragged_dot.json).
+_CONFIG_FIELDS = ("block_m", "block_n", "block_k", "num_stages", "split_k", "split_m", "persistent",
+                  "async_store", "post_scale", "collective", "grid_minor_dim", "grid_tile_width")
+_SHORT = {v: k for k, v in _DTYPES.items()}
+
+
+def _array(v) -> str:
   if isinstance(v, torch.Tensor):
-    return op_lib.ShapeDtype(tuple(v.shape), v.dtype).short()
+    v = op_lib.ShapeDtype(tuple(v.shape), v.dtype)
+  return v.short()
+
+
+def _encode(name: str, v: Any, arguments: dict) -> Any:
+  from tokamax_b200.ragged_dot.base import GroupSizes, RaggedDotDimensionNumbers
+  if isinstance(v, (op_lib.ShapeDtype, torch.Tensor)):
+    if name == "group_sizes":   # a bare array: what `bind` would make of it
+      total = int(arguments["lhs"].shape[0])
+      return {"num_groups": int(v.shape[0]), "total_size": total}
+    return _array(v)
   if isinstance(v, GroupSizes):
-    return {"group_sizes": v.to_json()}
+    return v.to_json()
   if isinstance(v, RaggedDotDimensionNumbers):
-    return {"dims": [v.dot_dimension_numbers, v.lhs_ragged_dimensions, v.rhs_group_dimensions]}
+    (lc, rc), (lb, rb) = v.dot_dimension_numbers
+    return {"dot_dimension_numbers": [[list(lc), list(rc)], [list(lb), list(rb)]],
+            "lhs_ragged_dimensions": list(v.lhs_ragged_dimensions),
+            "rhs_group_dimensions": list(v.rhs_group_dimensions)}
   if isinstance(v, torch.dtype):
-    return {"dtype": str(v).replace("torch.", "")}
+    return _SHORT.get(v, str(v).replace("torch.", ""))
   if hasattr(v, "qvalue") and hasattr(v, "scale"):
-    return {"qvalue": _encode(v.qvalue), "scale": _encode(v.scale)}
+    return {"qvalue": _array(v.qvalue), "scale": _array(v.scale)}
+  if name == "precision":
+    p = "DEFAULT" if v is None else str(getattr(v, "name", v)).upper()
+    return [p, p]
+  if callable(v):
+    return getattr(v, "__name__", type(v).__name__)
   return v
 
 
 def spec_to_json(arguments: dict) -> str:
-  """Serialises bound arguments (arrays as `bf16[M,K]` strings) to a canonical JSON key."""
-  skip = ("return_residuals",)
-  d = {k: _encode(v) for k, v in arguments.items() if k not in skip and v is not None and not callable(v)}
-  return json.dumps(d, sort_keys=True, separators=(",", ":"))
+  """Serialises bound arguments to a cache key in the reference's wire format
+  (tokamax/_src/autotuning/cache.py:37-49 with the field serialisers of
+  tokamax/_src/pydantic.py:245-352 and ops/ragged_dot/base.py:139-170): arrays as `bf16[M,K]`
+  strings, group sizes as `{"num_groups", "total_size"}` or the representative list, named
+  dimension-number fields, `precision` as a pair of names, then the keyword arguments the
+  reference's GPU backends do not have (only those that are set)."""
+  d = {}
+  for k in _KEY_FIELDS:
+    v = arguments.get(k)
+    if k == "precision":
+      d[k] = _encode(k, v, arguments)
+    elif k == "return_residuals":
+      d[k] = False       # never part of the tuning problem
+    else:
+      d[k] = None if v is None else _encode(k, v, arguments)
+  defaults = {"maybe_quantize_lhs": False, "zero_initialize": True}
+  for k in sorted(arguments):
+    v = arguments[k]
+    if k in _KEY_FIELDS or v is None or defaults.get(k, object()) == v:
+      continue
+    d[k] = _encode(k, v, arguments)
+  return json.dumps(d, separators=(",", ":"))
 
 
-def _decode(v: Any) -> Any:
+def _decode(name: str, v: Any) -> Any:
   from tokamax_b200.ragged_dot.base import GroupSizes, RaggedDotDimensionNumbers
   if isinstance(v, str) and (m := re.fullmatch(r"(\w+)\[([\d,]*)\]", v)) and m.group(1) in _DTYPES:
     shape = tuple(int(s) for s in m.group(2).split(",") if s)
     return op_lib.ShapeDtype(shape, _DTYPES[m.group(1)])
-  if isinstance(v, dict):
-    if "group_sizes" in v:
-      return GroupSizes.from_json(v["group_sizes"])
-    if "dims" in v:
-      d = v["dims"]
-      return RaggedDotDimensionNumbers(d[0], d[1], d[2])
-    if "dtype" in v:
-      return getattr(torch, v["dtype"])
-    if "qvalue" in v and "scale" in v:
-      from tokamax_b200.quantization import QArray
-      return QArray(_decode(v["qvalue"]), _decode(v["scale"]))
+  if name == "group_sizes":
+    return GroupSizes.from_json(v)
+  if name == "ragged_dot_dimension_numbers":
+    d = v["dot_dimension_numbers"]
+    return RaggedDotDimensionNumbers(((d[0][0], d[0][1]), (d[1][0], d[1][1])), v["lhs_ragged_dimensions"],
+                                     v["rhs_group_dimensions"])
+  if name == "precision":
+    ps = {str(p).upper() for p in (v if isinstance(v, list) else [v])}
+    return None if ps <= {"DEFAULT", "NONE"} else ps.pop().lower()
+  if name == "preferred_element_type" and isinstance(v, str):
+    return _DTYPES.get(v) or getattr(torch, v)
+  if isinstance(v, dict) and "qvalue" in v and "scale" in v:
+    from tokamax_b200.quantization import QArray
+    return QArray(_decode("", v["qvalue"]), _decode("", v["scale"]))
   return v
 
 
 def spec_from_json(s: str) -> dict:
-  return {k: _decode(v) for k, v in json.loads(s).items()}
+  """Keyword arguments for `op.bind` from a cache key.  `activation` names are dropped (the
+  callable cannot be rebuilt; it is not part of the in-memory cache key either)."""
+  out = {k: _decode(k, v) for k, v in json.loads(s).items() if v is not None}
+  out.pop("activation", None)
+  out.pop("return_residuals", None)
+  return out
 
 
 def config_to_json(config) -> str:
   d = dataclasses.asdict(config)
-  return json.dumps({k: (int(v) if hasattr(v, "value") else v) for k, v in d.items()},
-                    sort_keys=True, separators=(",", ":"))
+  d.setdefault("async_store", False)     # field of the shipped reference caches' schema
+  out = {k: (int(d[k]) if hasattr(d[k], "value") else d[k]) for k in _CONFIG_FIELDS}
+  for k in sorted(d):                    # fields newer than those files, only when set
+    if k not in out and d[k] is not None:
+      out[k] = d[k]
+  return json.dumps(out, separators=(",", ":"))
+
+
+def config_from_json(config_cls, s: str):
+  """A Config from its JSON, ignoring fields this Config class does not have."""
+  known = {f.name for f in dataclasses.fields(config_cls)}
+  return config_cls(**{k: v for k, v in json.loads(s).items() if k in known})
 
 
 class AutotuningCache(dict):
@@ -119,7 +180,7 @@ class AutotuningCache(dict):
         try:
           ba = self.op.bind(**spec_from_json(spec_json))
           data = autotuner.AutotuningData({
-              self.op.config_cls(**json.loads(cfg)): benchmarking.BenchmarkData.fromdict(bd)
+              config_from_json(self.op.config_cls, cfg): benchmarking.BenchmarkData.fromdict(bd)
               for cfg, bd in entries.items()})
           out[ba.autotuning_cache_key] = data
         except Exception:

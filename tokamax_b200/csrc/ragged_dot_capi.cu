@@ -824,9 +824,20 @@ int tkmx_ragged_dot_drhs(const void* lhs, const void* dout, const int32_t* group
                          int64_t g, int in_dtype, int out_dtype, const tkmx_config* config,
                          void* cuda_stream) {
   (void)workspace; (void)workspace_bytes;
+  return tkmx_ragged_dot_drhs_window(lhs, dout, group_sizes, drhs, m, k, n, g, 0, g, in_dtype, out_dtype, config,
+                                     cuda_stream);
+}
+
+int tkmx_ragged_dot_drhs_window(const void* lhs, const void* dout, const int32_t* group_sizes, void* drhs,
+                                int64_t m, int64_t k, int64_t n, int64_t g, int64_t group_begin,
+                                int64_t group_count, int in_dtype, int out_dtype, const tkmx_config* config,
+                                void* cuda_stream) {
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (m < 0 || k < 0 || n < 0 || g < 0) return TKMX_ERR_INVALID_ARGUMENT;
-  if (!fits_i32(m) || !fits_i32(k) || !fits_i32(n) || !fits_i32(g)) return TKMX_ERR_TOO_LARGE;
+  if (group_begin < 0 || group_count < 0 || group_begin + group_count > g) return TKMX_ERR_INVALID_ARGUMENT;
+  const int64_t g_all = g;   // groups the offsets are counted over
+  g = group_count;           // slabs of the output
+  if (!fits_i32(m) || !fits_i32(k) || !fits_i32(n) || !fits_i32(g_all)) return TKMX_ERR_TOO_LARGE;
   if (in_dtype != TKMX_BF16 && in_dtype != TKMX_F16) return TKMX_ERR_UNSUPPORTED;
   if (out_dtype != TKMX_BF16 && out_dtype != TKMX_F16 && out_dtype != TKMX_F32)
     return TKMX_ERR_UNSUPPORTED;
@@ -843,7 +854,7 @@ int tkmx_ragged_dot_drhs(const void* lhs, const void* dout, const int32_t* group
   int st = get_device_info(&dev);
   if (st != TKMX_OK) return st;
   ResolvedConfig rc;
-  st = resolve_config(config, n, int(g), false, *dev, &rc);
+  st = resolve_config(config, n, int(g_all), false, *dev, &rc);
   if (st != TKMX_OK) return st;
   const int64_t tile_m = rc.pair ? 256 : 128;
   const int64_t r_tiles = (k + tile_m - 1) / tile_m;
@@ -874,10 +885,10 @@ int tkmx_ragged_dot_drhs(const void* lhs, const void* dout, const int32_t* group
   p.rows = int32_t(k);
   p.cols = int32_t(n);
   p.cdim = 0;
-  p.num_groups = int32_t(g);
-  p.rhs_groups = int32_t(g);
-  p.group_begin = 0;
-  p.group_end = int32_t(g);
+  p.num_groups = int32_t(g_all);
+  p.rhs_groups = int32_t(g_all);
+  p.group_begin = int32_t(group_begin);
+  p.group_end = int32_t(group_begin + group_count);
   p.out_is_f32 = out_dtype == TKMX_F32;
   p.out_is_f16 = out_dtype == TKMX_F16;
   p.out_vec_ok = ((n * elt_size(out_dtype)) % 16 == 0) &&
@@ -891,7 +902,7 @@ int tkmx_ragged_dot_drhs(const void* lhs, const void* dout, const int32_t* group
   // drhs tiles are as long as their group has rows: with short ones (~512 rows, 3 us per tile)
   // the per-tile hand-off costs more than the balance gains (-3 %), with long ones it wins
   // (+2 ... +6 % at 1024-2048 rows per group).
-  assign_sched(*dev, &p, g > 0 && m / g >= 768);
+  assign_sched(*dev, &p, g_all > 0 && m / g_all >= 768);
 
   CUtensorMap mo = {};
   p.tma_store = 0;

@@ -342,6 +342,7 @@ struct TileWalker {
   int total_real, total_tiles;
   int next, stride;
   int cursor;  // rows modes: current position in the visiting order
+  int group_begin = 0;  // contract mode: first group of the window that is computed
   int cycles, rhs_groups;
   const int* order = nullptr;  // rows modes: explicit visiting order (smem), or null for the cyclic rule
   // Rows modes with swapped short tiles (pair mode): a group that needs several row tiles is cut
@@ -363,7 +364,8 @@ struct TileWalker {
     n_tiles = (cols + kBlockN - 1) / kBlockN;
     if constexpr (kMode == kContract) {
       const int r_tiles = (rows + kTileM - 1) / kTileM;
-      total_real = num_groups * r_tiles * n_tiles;
+      group_begin = p.group_begin;
+      total_real = (p.group_end - p.group_begin) * r_tiles * n_tiles;   // only the window's groups
       total_tiles = total_real;
     } else {
       total_real = tile_start[num_groups] * n_tiles;
@@ -406,8 +408,9 @@ struct TileWalker {
     if constexpr (kMode == kContract) {
       const int r_tiles = (rows + kTileM - 1) / kTileM;
       const int per_group = r_tiles * n_tiles;
-      const int g = lin / per_group;
-      const int local = lin - g * per_group;
+      const int g_local = lin / per_group;
+      const int g = group_begin + g_local;
+      const int local = lin - g_local * per_group;
       int mi, ni;
       if (minor_is_m) raster(local, r_tiles, n_tiles, mi, ni);
       else raster(local, n_tiles, r_tiles, ni, mi);
@@ -1087,7 +1090,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
       size_t out_row_off;
       if constexpr (kMode == kContract)
-        out_row_off = (static_cast<size_t>(t.group) * p.rows + row) * ld_out;
+        out_row_off = (static_cast<size_t>(t.group - p.group_begin) * p.rows + row) * ld_out;
       else
         out_row_off = static_cast<size_t>(row) * ld_out;
       const float* scale_row = nullptr;
@@ -1297,7 +1300,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           __syncwarp();
           if (lane == 0) {
             const uint32_t src = base + L.staging + ew * kStagingBytes;
-            if constexpr (kMode == kContract) ptx::tma_store_3d(&map_out, src, col, warp_row0, t.group);
+            if constexpr (kMode == kContract) ptx::tma_store_3d(&map_out, src, col, warp_row0, t.group - p.group_begin);
             else ptx::tma_store_2d(&map_out, src, col, warp_row0);
             ptx::bulk_commit_group();
           }

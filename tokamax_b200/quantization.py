@@ -77,8 +77,37 @@ def quantize_per_channel(w: torch.Tensor, qtype: torch.dtype) -> QArray:
   return QArray(q.contiguous(), scale.to(torch.float32).contiguous())
 
 
+@dataclasses.dataclass(frozen=True)
+class AsQArray:
+  """An array that is to be quantised before the computation, so that the quantisation can
+  happen next to (or inside) the kernel (tokamax/_src/quantization.py:39-72).  Here only the
+  scheme the kernels take exists: weights [G, K, N] with one scale per expert and output
+  channel, i.e. channelwise axes (0, 2); `calibration_method` "absmax"."""
+
+  value: torch.Tensor
+  qtype: torch.dtype
+  channelwise_axes: tuple = (0, 2)
+  tiled_axes: dict | None = None
+  calibration_method: str = "absmax"
+
+  shape = property(lambda self: self.value.shape)
+  dtype = property(lambda self: self.value.dtype)
+  ndim = property(lambda self: self.value.ndim)
+
+  def as_qarray(self) -> QArray:
+    if tuple(sorted(self.channelwise_axes)) != (0, 2) or self.tiled_axes or self.calibration_method != "absmax":
+      raise NotImplementedError("AsQArray: per-(expert, output-channel) absmax quantisation only")
+    return quantize_per_channel(self.value, self.qtype)
+
+
+def as_array_or_qarray(x):
+  """Quantises an AsQArray now; passes tensors and QArrays through (quantization.py:81-84)."""
+  return x.as_qarray() if isinstance(x, AsQArray) else x
+
+
 def as_array(x):
   """Dequantises a QArray (qvalue * scale in the scale dtype); passes tensors through."""
+  x = as_array_or_qarray(x)
   if isinstance(x, QArray):
     s = x.scale if x.scale.ndim == x.qvalue.ndim else x.scale[:, None, :]
     return x.qvalue.to(s.dtype) * s

@@ -156,6 +156,8 @@ def _as_int32_device(gs, device) -> torch.Tensor:
 
 def _normalize_rhs(rhs, rhs_scale):
   """Returns (rhs values [G,K,N], per-channel scale [G,N] or None)."""
+  from tokamax_b200.quantization import as_array_or_qarray
+  rhs = as_array_or_qarray(rhs)     # an AsQArray is quantised here, next to the kernel call
   if isinstance(rhs, QArray):
     if rhs_scale is not None:
       raise ValueError("rhs_scale given together with a quantised rhs")
@@ -184,6 +186,10 @@ class B200RaggedDot(base.RaggedDot):
   # activations split into two e4m3 terms (needs 2*M*K bytes of scratch per call); False
   # expands the weights to bf16 inside the kernel and multiplies in bf16 (no scratch).
   native_fp8: bool = True
+  # Local weight group count of the drhs (ragged-contracting) call under expert parallelism:
+  # `group_sizes` then counts the global groups and the result holds the `num_actual_groups`
+  # groups starting at `group_offset` (pallas_mosaic_tpu_v2.py:89-93 upstream).
+  num_actual_groups: int | None = None
 
   def __post_init__(self):
     if self.vjp is None:
@@ -229,8 +235,11 @@ class B200RaggedDot(base.RaggedDot):
       if bias.ndim != 2:
         raise ValueError("rhs_bias must have shape [G, 1, N] or [G, N]")
     windowed = group_offset is not None or not zero_initialize
-    if windowed and ragged_dot_dimension_numbers != base.DEFAULT_RAGGED_DOT_DIM_NUMS:
-      raise NotImplementedError("group_offset / zero_initialize=False: default dimension numbers only")
+    drhs_window = (ragged_dot_dimension_numbers == base.RAGGED_CONTRACTING_DOT_DIM_NUMS
+                   and (group_offset is not None or self.num_actual_groups is not None) and zero_initialize)
+    if windowed and not drhs_window and ragged_dot_dimension_numbers != base.DEFAULT_RAGGED_DOT_DIM_NUMS:
+      raise NotImplementedError("group_offset / zero_initialize=False: default or ragged-contracting "
+                                "dimension numbers only")
     if isinstance(lhs, QArray):
       raise NotImplementedError("quantised lhs is not supported")
     rhs, scale = _normalize_rhs(rhs, rhs_scale)
@@ -329,8 +338,19 @@ class B200RaggedDot(base.RaggedDot):
         raise NotImplementedError("quantised rhs with ragged-contracting dimension numbers")
       if lhs.ndim != 2 or rhs.ndim != 2 or lhs.shape[0] != rhs.shape[0]:
         raise ValueError(f"incompatible shapes {tuple(lhs.shape)} and {tuple(rhs.shape)}")
-      out = torch.empty((gs.shape[0], lhs.shape[1], rhs.shape[1]), dtype=out_dtype, device=lhs.device)
-      _capi.ragged_dot_drhs(lhs, rhs, gs, out, config=ccfg)
+      if drhs_window:
+        # Expert-parallel shard: global group_sizes, the local experts' slabs only
+        # (reference_tgmm, gmm_v2_test.py:109-160).  group_offset is read on the host.
+        begin = 0 if group_offset is None else int(torch.as_tensor(group_offset).reshape(-1)[0])
+        count = self.num_actual_groups if self.num_actual_groups is not None else gs.shape[0] - begin
+        if begin < 0 or count < 0 or begin + count > gs.shape[0]:
+          raise ValueError(f"group_offset ({begin}) + num_actual_groups ({count}) exceeds the "
+                           f"{gs.shape[0]} entries of group_sizes")
+        out = torch.empty((count, lhs.shape[1], rhs.shape[1]), dtype=out_dtype, device=lhs.device)
+        _capi.ragged_dot_drhs(lhs, rhs, gs, out, config=ccfg, group_begin=begin)
+      else:
+        out = torch.empty((gs.shape[0], lhs.shape[1], rhs.shape[1]), dtype=out_dtype, device=lhs.device)
+        _capi.ragged_dot_drhs(lhs, rhs, gs, out, config=ccfg)
     else:
       raise NotImplementedError(f"unsupported ragged dot dimension numbers: {dims}")
 
@@ -372,7 +392,18 @@ class B200RaggedDot(base.RaggedDot):
   # ------------------------------------------------------------------ configs
   def _get_autotuning_cache_key(self, ba: op_lib.BoundArguments):
     skip = ("return_residuals",)
-    return tuple((k, op_lib.abstractify(v)) for k, v in ba.arguments.items()
+
+    def key_of(k, v):
+      if k == "group_sizes":
+        # One form whether the caller passed an array or a GroupSizes: (groups, representative
+        # sizes or total rows).  A bare array stands for "rows of lhs spread over the groups",
+        # which is what `bind` makes of it for the default dimension numbers.
+        if isinstance(v, GroupSizes):
+          return ("group_sizes", int(v.value.shape[0]), v.repr_value_or_total_size)
+        return ("group_sizes", int(v.shape[0]), int(ba.arguments["lhs"].shape[0]))
+      return op_lib.abstractify(v)
+
+    return tuple((k, key_of(k, v)) for k, v in ba.arguments.items()
                  if k not in skip and v is not None and not callable(v))
 
   def _get_heuristics_config(self, ba: op_lib.BoundArguments) -> Config:

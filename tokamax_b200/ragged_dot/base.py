@@ -210,8 +210,14 @@ def vjp(residuals, out, dout, lhs, rhs, *, group_sizes, ragged_dot_dimension_num
                        lhs_quantization_dtype=lhs_quantization_dtype,
                        rhs_quantization_dtype=rhs_quantization_dtype,
                        where="the ragged_dot backward path")
-  if isinstance(rhs, QArray) or isinstance(lhs, QArray):
-    raise NotImplementedError("gradients with respect to quantised operands are not defined")
+  if isinstance(lhs, QArray):
+    raise NotImplementedError("gradients with respect to a quantised lhs are not defined")
+  rhs_is_quantised = isinstance(rhs, QArray)
+  if rhs_is_quantised:
+    # The reference's vjp hands the quantised rhs on to the dlhs product (base.py:434-446);
+    # here it is dequantised for it.  A quantised array has no gradient of its own.
+    from tokamax_b200.quantization import as_array
+    rhs = as_array(rhs).to(lhs.dtype)
 
   if activation is not None:
     # d(activation)/d(pre-activation) applied to dout (base.py:412-414).
@@ -241,6 +247,8 @@ def vjp(residuals, out, dout, lhs, rhs, *, group_sizes, ragged_dot_dimension_num
   dlhs = dlhs_ragged_dot(dout, rhs, group_sizes=group_sizes,
                          ragged_dot_dimension_numbers=dlhs_dims, precision=precision,
                          preferred_element_type=lhs.dtype)
+  if rhs_is_quantised:
+    return dlhs, None
   drhs_dims = RaggedDotDimensionNumbers(
       ((lhs_kept, dout_lhs_kept), (lhs_batch, dout_batch)), lhs_ragged, [])
   drhs = drhs_ragged_dot(lhs, dout, group_sizes=group_sizes,
