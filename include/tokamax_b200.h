@@ -161,6 +161,24 @@ TKMX_API int tkmx_ragged_dot_fwd_epilogue(const void* lhs, const void* rhs, cons
                                           const tkmx_config* config, void* cuda_stream);
 
 /*
+ * Forward with the output quantised in the epilogue: tmp = act(ragged_dot(lhs, rhs) + rhs_bias)
+ * in float32, then per row and block of `subchannel` columns (64, 128 or 256; divides n and
+ * the tile width) scale = max|tmp| / 448 (1 for an all-zero block) and
+ * q = e4m3(clip(tmp / scale, -448, 448)): out_q uint8 [m, n] (e4m3 bits), out_scale float
+ * [m, n / subchannel].  Rows of no group give q = 0, scale = 1.  The float32 product never
+ * reaches memory.  Replaces the fused epilogue quantisation of the reference's Blackwell
+ * quant kernel (`epilogue_quant_qtype` / `epilogue_quant_subchannel_size`,
+ * tokamax/_src/ops/ragged_dot/pallas_mosaic_gpu_common.py:63-68; rule of
+ * pallas_mosaic_gpu_kernel_sm100_fp8_quant.py:800-844), here on the 16-bit kernel.
+ * activation: 0 or TKMX_ACT_*.
+ */
+TKMX_API int tkmx_ragged_dot_fwd_quant_out(const void* lhs, const void* rhs, const int32_t* group_sizes,
+                                           const float* rhs_bias, void* out_q, float* out_scale, int64_t m,
+                                           int64_t k, int64_t n, int64_t g, int in_dtype, int rhs_layout,
+                                           int activation, int subchannel, const tkmx_config* config,
+                                           void* cuda_stream);
+
+/*
  * dlhs[i, :] = dout[i, :] @ rhs[group(i)]^T  (contraction over n; rhs read as stored,
  * no transpose pass).  Replaces the dlhs_ragged_dot call of `vjp`
  * (tokamax/_src/ops/ragged_dot/base.py:434-446, TRANS_RHS dimension numbers

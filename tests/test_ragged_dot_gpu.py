@@ -1258,9 +1258,10 @@ def test_as_qarray_and_vjp_with_quantised_rhs(tk, capi):
   lhs, w, dout, _ = helpers.seeded_inputs("asq", m, k, n, g, scale=0.3)
   gs = np.array([100, 200, 12, 200], np.int32)
   for qtype in (torch.float8_e4m3fn, torch.int8):
-    q, scale = ref.quantize_tensor_ref(w, qtype)
-    want = ref.ragged_dot_ref(lhs, q, gs, rhs_scale=scale, out_dtype=torch.float32)
-    out = tk.ragged_dot(lhs.cuda(), tk.AsQArray(w.cuda(), qtype), _gs_dev(gs))
+    lazy = tk.AsQArray(w.cuda(), qtype)
+    qa = lazy.as_qarray()       # the same (q, scale) goes to the oracle: the quantiser is not under test
+    want = ref.ragged_dot_ref(lhs, qa.qvalue.cpu(), gs, rhs_scale=qa.channel_scale().cpu(), out_dtype=torch.float32)
+    out = tk.ragged_dot(lhs.cuda(), lazy, _gs_dev(gs))
     helpers.assert_close(out, want, atol=helpers.Q_ATOL, rtol=helpers.Q_RTOL, what=f"AsQArray {qtype}")
   qa = tk.quantize_per_channel(w.cuda(), torch.float8_e4m3fn)
   a = lhs.cuda().requires_grad_(True)
@@ -1269,3 +1270,60 @@ def test_as_qarray_and_vjp_with_quantised_rhs(tk, capi):
   deq = (qa.qvalue.float() * qa.scale.float()).bfloat16()
   want_dl = ref.ragged_dot_ref(dout, deq.cpu(), gs, dims=ref.TRANS_RHS, out_dtype=torch.float32)
   helpers.assert_close(dl, want_dl, atol=helpers.Q_ATOL, rtol=helpers.Q_RTOL, what="dlhs with quantised rhs")
+
+
+# ---------------------------------------------------------------- fused output quantisation
+@pytest.mark.parametrize("sub", [64, 128, 256])
+@pytest.mark.parametrize("collective,act", [(0, None), (1, "relu"), (1, None)])
+def test_fused_output_quantisation(capi, sub, collective, act):
+  """The epilogue returns (q, scale) by the reference's rule
+  (pallas_mosaic_gpu_kernel_sm100_fp8_quant.py:800-844): per row and `sub` columns
+  scale = max|x| / 448, q = e4m3(x / scale).  Scales against the float32 oracle; q * scale
+  against the oracle within e4m3's 2^-4 relative step of the block maximum; empty rows q = 0,
+  scale = 1."""
+  g, m, k, n = 5, 1100, 192, 512
+  lhs, rhs, _, _ = helpers.seeded_inputs(f"quant-out-{sub}", m, k, n, g, scale=0.3)
+  gs = np.array([300, 0, 260, 77, 400], np.int32)           # 63 rows of no group
+  q = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda").to(torch.float8_e4m3fn)
+  qs = torch.full((m, n // sub), float("nan"), dtype=torch.float32, device="cuda")
+  capi.ragged_dot_fwd_quant_out(lhs.cuda(), rhs.cuda(), _gs_dev(gs), q, qs, sub, element_activation=act,
+                                config=capi.Config(block_n=256, collective=collective))
+  capi.device_status()
+  pre = ref.ragged_dot_ref(lhs, rhs, gs, out_dtype=torch.float32)
+  if act == "relu":
+    pre = torch.relu(pre)
+  blocks = pre.reshape(m, n // sub, sub)
+  amax = blocks.abs().amax(dim=2)
+  want_scale = torch.where(amax == 0, torch.ones(()), amax / 448.0)
+  torch.testing.assert_close(qs.cpu(), want_scale, rtol=1e-4, atol=1e-7)
+  deq = (q.float().cpu().reshape(m, n // sub, sub) * qs.cpu()[:, :, None])
+  err = (deq - blocks).abs()
+  assert bool((err <= amax[:, :, None] * 2.0 ** -4 + 1e-6).all()), float(err.max())
+  rows = int(gs.sum())
+  assert (q[rows:].float() == 0).all() and (qs[rows:] == 1).all()
+
+
+def test_chained_ragged_dots_through_a_quantised_intermediate(tk, capi):
+  """dot1 with `epilogue_quant_qtype` returns a QArray that dot2 consumes as its lhs; against
+  the chain with a bf16 intermediate (the reference's chained test,
+  pallas_mosaic_gpu_kernel_sm100_fp8_quant_test.py:490-553: relative mean error < 0.1)."""
+  from tokamax_b200.ragged_dot import api
+  from tokamax_b200.ragged_dot import b200 as b200_lib
+  g, m, k, n = 8, 512, 256, 512
+  lhs, w1, _, rng = helpers.seeded_inputs("chain", m, k, n, g, scale=0.2)
+  w2 = torch.from_numpy(rng.normal(0, 0.05, (g, n, n)).astype(np.float32)).bfloat16()
+  gs = np.asarray(tk.generate_ragged_dot_group_sizes(m=m, num_groups=g), np.int32)
+  gsd = _gs_dev(gs)
+  op = api.IMPLEMENTATIONS["b200"]
+  cfg = b200_lib.Config(block_m=128, block_n=256, block_k=64, num_stages=4,
+                        epilogue_quant_qtype=torch.float8_e4m3fn, epilogue_quant_subchannel_size=128)
+  fused_op = b200_lib.B200RaggedDot(config=cfg)
+  h = fused_op(lhs.cuda(), w1.cuda(), group_sizes=gsd, activation=torch.relu)
+  assert isinstance(h, tk.QArray) and h.qvalue.dtype == torch.float8_e4m3fn
+  assert tuple(h.scale.shape) == (m, n // 128)
+  y_fused = op(h, w2.cuda(), group_sizes=gsd)
+  h_plain = op(lhs.cuda(), w1.cuda(), group_sizes=gsd, activation=torch.relu)
+  y_base = op(h_plain, w2.cuda(), group_sizes=gsd)
+  count = int(gs.sum())
+  f, b = y_fused[:count].float(), y_base[:count].float()
+  assert float((f - b).abs().mean() / b.abs().mean().clamp(min=1e-6)) < 0.1

@@ -64,6 +64,7 @@ EXPORTED_SYMBOLS = (
     "tkmx_ep_moe_fused",
     "tkmx_cross_rank_barrier",
     "tkmx_ragged_dot_drhs_window",
+    "tkmx_ragged_dot_fwd_quant_out",
 )
 
 
@@ -120,6 +121,9 @@ def load() -> ctypes.CDLL:
     for fn in (lib.tkmx_ragged_dot_dlhs, lib.tkmx_ragged_dot_drhs):
       fn.restype = ctypes.c_int
       fn.argtypes = [vp, vp, vp, vp, vp, sz, i64, i64, i64, i64, ctypes.c_int, ctypes.c_int, cfgp, vp]
+    lib.tkmx_ragged_dot_fwd_quant_out.restype = ctypes.c_int
+    lib.tkmx_ragged_dot_fwd_quant_out.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, ctypes.c_int,
+                                                  ctypes.c_int, ctypes.c_int, ctypes.c_int, cfgp, vp]
     lib.tkmx_ragged_dot_drhs_window.restype = ctypes.c_int
     lib.tkmx_ragged_dot_drhs_window.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, ctypes.c_int,
                                                 ctypes.c_int, cfgp, vp]
@@ -292,6 +296,28 @@ def ragged_dot_fwd_epilogue(lhs, rhs, group_sizes, out, *, rhs_scale=None, rhs_b
         ELEMENT_ACTIVATIONS[element_activation] if element_activation is not None
         else (0 if activation is None else GATEUP_ACTIVATIONS[activation]), _cfg(config), _stream(dev))
   check(st, "tkmx_ragged_dot_fwd_epilogue")
+
+
+def ragged_dot_fwd_quant_out(lhs, rhs, group_sizes, out_q, out_scale, subchannel: int, *, rhs_bias=None,
+                             element_activation: str | None = None, rhs_layout=RHS_GKN,
+                             config: Config | None = None) -> None:
+  """Forward whose epilogue quantises the result: out_q float8_e4m3fn [m, n], out_scale float32
+  [m, n / subchannel] (scale = max|x| / 448 per row and block of `subchannel` columns)."""
+  dev = _require_cuda(lhs, rhs, group_sizes, out_q, out_scale, rhs_bias)
+  if out_q.dtype != torch.float8_e4m3fn or out_scale.dtype != torch.float32:
+    raise ValueError("out_q must be float8_e4m3fn and out_scale float32")
+  if element_activation is not None and element_activation not in ELEMENT_ACTIVATIONS:
+    raise NotImplementedError(f"Unsupported activation function: {element_activation}")
+  m, k = lhs.shape
+  g = rhs.shape[0]
+  n = rhs.shape[2] if rhs_layout == RHS_GKN else rhs.shape[1]
+  with torch.cuda.device(dev):
+    st = load().tkmx_ragged_dot_fwd_quant_out(
+        _ptr(lhs), _ptr(rhs), _ptr(group_sizes), _ptr(rhs_bias), _ptr(out_q), _ptr(out_scale), m, k, n, g,
+        dtype_code(lhs.dtype), rhs_layout,
+        0 if element_activation is None else ELEMENT_ACTIVATIONS[element_activation], subchannel,
+        _cfg(config), _stream(dev))
+  check(st, "tkmx_ragged_dot_fwd_quant_out")
 
 
 def ragged_dot_fwd_cyclic(lhs, rhs, group_sizes, out, *, rhs_scale=None, rhs_layout=RHS_GKN,

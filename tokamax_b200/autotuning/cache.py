@@ -140,7 +140,7 @@ def config_to_json(config) -> str:
   out = {k: (int(d[k]) if hasattr(d[k], "value") else d[k]) for k in _CONFIG_FIELDS}
   for k in sorted(d):                    # fields newer than those files, only when set
     if k not in out and d[k] is not None:
-      out[k] = d[k]
+      out[k] = str(d[k]).replace("torch.", "") if isinstance(d[k], torch.dtype) else d[k]
   return json.dumps(out, separators=(",", ":"))
 
 

@@ -328,8 +328,19 @@ int run_rows(const void* a, const void* b, bool b_cols_contiguous, const int32_t
              const float* col_scale, void* out, int64_t m, int64_t cdim, int64_t cols, int64_t g,
              int64_t g_rhs, int in_dtype, int b_dtype, int out_dtype, const tkmx_config* config,
              cudaStream_t stream, bool zero_initialize = true, int64_t group_begin = 0,
-             int64_t group_count = -1, int gateup = 0, const float* col_bias = nullptr) {
+             int64_t group_count = -1, int gateup = 0, const float* col_bias = nullptr,
+             float* out_scales = nullptr, int quant_sub = 0) {
   if (g_rhs <= 0 && g > 0) return TKMX_ERR_INVALID_ARGUMENT;
+  if (quant_sub != 0) {
+    // Fused output quantisation: e4m3 values and one float scale per row and quant_sub columns.
+    if (out_dtype != TKMX_F8E4M3 || out_scales == nullptr) return TKMX_ERR_INVALID_ARGUMENT;
+    if (quant_sub != 64 && quant_sub != 128 && quant_sub != 256) return TKMX_ERR_UNSUPPORTED;
+    if (cols % quant_sub != 0 || (gateup > 0 && gateup < TKMX_ACT_RELU)) return TKMX_ERR_UNSUPPORTED;
+    if (g == 0 || cdim == 0 || m == 0) return TKMX_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0 || (reinterpret_cast<uintptr_t>(out_scales) & 3u) != 0)
+      return TKMX_ERR_ALIGNMENT;
+    out_dtype = TKMX_BF16;   // for the checks below; the epilogue writes bytes
+  }
   // Codes from TKMX_ACT_RELU up are elementwise activations on the float32 result; the codes
   // below them are the gate/up forms.
   int element_act = 0;
@@ -374,6 +385,7 @@ int run_rows(const void* a, const void* b, bool b_cols_contiguous, const int32_t
   st = resolve_config(config, cols, int(g), true, *dev, &rc);
   if (st != TKMX_OK) return st;
   if (gateup && rc.block_n < 128) return TKMX_ERR_UNSUPPORTED;  // each half needs whole 64-column boxes
+  if (quant_sub != 0 && rc.block_n % quant_sub != 0) return TKMX_ERR_UNSUPPORTED;
 
   CUtensorMap ma, mb;
   {
@@ -430,7 +442,9 @@ int run_rows(const void* a, const void* b, bool b_cols_contiguous, const int32_t
   // Pair mode, 256-column tiles: a group's last tile with at most this many rows runs with
   // swapped MMA operands (cost follows its rows).  192 = where the swapped MMA stops being
   // cheaper than the full one (measured 141 against 173 cycles).  TKMX_SWAP_ROWS overrides.
-  p.swap_rows = (rc.pair && rc.block_n == 256 && !gateup) ? env_int("TKMX_SWAP_ROWS", 192, 0, 192) : 0;
+  p.swap_rows = (rc.pair && rc.block_n == 256 && !gateup && quant_sub == 0) ? env_int("TKMX_SWAP_ROWS", 192, 0, 192) : 0;
+  p.out_scales = out_scales;
+  p.quant_sub = quant_sub;
   // Equal swapped tiles instead of full + short ones: off by default.  Measured on B200 it
   // lost (cfg4: 0.40 against 0.24 ms): a swapped tile's transposed epilogue stores 2 bytes per
   // lane and grows with the tile's rows, which outweighs the MMA time saved.
@@ -439,7 +453,7 @@ int run_rows(const void* a, const void* b, bool b_cols_contiguous, const int32_t
   // 16-bit outputs: blocks of 32 rows x 64 columns that are not ragged leave by TMA store.
   CUtensorMap mo = {};
   p.tma_store = 0;
-  if (out_dtype != TKMX_F32 && p.out_vec_ok && !gateup && col_bias == nullptr) {
+  if (out_dtype != TKMX_F32 && p.out_vec_ok && !gateup && col_bias == nullptr && quant_sub == 0) {
     const uint64_t dims[2] = {uint64_t(cols), uint64_t(m)};
     const uint64_t strides[1] = {uint64_t(cols) * 2};
     const uint32_t box[2] = {64, 32};
@@ -794,6 +808,18 @@ int tkmx_ragged_dot_fwd_epilogue(const void* lhs, const void* rhs, const int32_t
   if (rhs_scale != nullptr) return TKMX_ERR_UNSUPPORTED;
   return run_rows(lhs, rhs, rhs_layout == TKMX_RHS_GKN, group_sizes, nullptr, out, m, k, n, g, g, lhs_dtype,
                   rhs_dtype, out_dtype, config, stream, true, 0, -1, activation, rhs_bias);
+}
+
+int tkmx_ragged_dot_fwd_quant_out(const void* lhs, const void* rhs, const int32_t* group_sizes,
+                                  const float* rhs_bias, void* out_q, float* out_scale, int64_t m, int64_t k,
+                                  int64_t n, int64_t g, int in_dtype, int rhs_layout, int activation,
+                                  int subchannel, const tkmx_config* config, void* cuda_stream) {
+  if (rhs_layout != TKMX_RHS_GKN && rhs_layout != TKMX_RHS_GNK) return TKMX_ERR_INVALID_ARGUMENT;
+  if (activation != 0 && (activation < TKMX_ACT_RELU || activation > TKMX_ACT_SIGMOID)) return TKMX_ERR_INVALID_ARGUMENT;
+  if (subchannel <= 0) return TKMX_ERR_INVALID_ARGUMENT;
+  return run_rows(lhs, rhs, rhs_layout == TKMX_RHS_GKN, group_sizes, nullptr, out_q, m, k, n, g, g, in_dtype,
+                  in_dtype, TKMX_F8E4M3, config, static_cast<cudaStream_t>(cuda_stream), true, 0, -1, activation,
+                  rhs_bias, out_scale, subchannel);
 }
 
 int tkmx_ragged_dot_fwd_cyclic(const void* lhs, const void* rhs, const int32_t* group_sizes,

@@ -52,6 +52,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include "ep_fused_sm100.cuh"
 #include "ptx_sm100.cuh"
@@ -103,6 +104,8 @@ struct RaggedGemmParams {
   int32_t mixed_order;         // fp8 kernel visiting order: 0 = by index, 1 = small and large groups merged, 2 = large groups first
   int32_t swap_rows;           // tiles with at most this many rows swap the MMA operands (0: never); see kernels
   int32_t balance_tiles;       // 1: cut multi-tile groups into equal swapped tiles where possible (see TileWalker)
+  float* out_scales;           // fused output quantisation: scales [M, cols / quant_sub], else null
+  int32_t quant_sub;           // columns per output scale (64, 128 or 256; divides the tile width), 0 = off
   int32_t* status;             // device status word (see DeviceStatus)
 };
 
@@ -1198,6 +1201,76 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             for (int i = 0; i < 32; ++i) vg[i] = 0u;
           }
           store_chunk(p, vg, nullptr, row_ok, out_row_off, out_col0 + c * 32, out_cols);
+        }
+        if (has_acc) {
+          ptx::tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kPair) ptx::mbar_arrive_remote(ptx::map_to_cta(bar_acc_empty + 8u * b, 0));
+            else ptx::mbar_arrive(bar_acc_empty + 8u * b);
+          }
+        }
+        continue;
+      }
+      if (kMode != kContract && p.quant_sub != 0) {
+        // Fused output quantisation (the rule of the reference's fp8 epilogue,
+        // pallas_mosaic_gpu_kernel_sm100_fp8_quant.py:800-844): per row and block of quant_sub
+        // columns, scale = max|x| / 448 (1 for an all-zero block), q = e4m3(clip(x / scale)).
+        // A thread owns a row: pass 1 finds the block's maximum, pass 2 reloads the
+        // accumulator, divides and stores 32 bytes per chunk.
+        const int sub = p.quant_sub;
+        const int blocks = min(kBlockN / sub, (p.cols - t.col0 + sub - 1) / sub);   // warp-uniform
+        uint8_t* qrow = reinterpret_cast<uint8_t*>(p.out) + static_cast<size_t>(row) * p.cols;
+        uint32_t v[32];
+#pragma unroll 1
+        for (int sb = 0; sb < blocks; ++sb) {
+          const int c0 = t.col0 + sb * sub;
+          float amax = 0.f;
+          auto load_chunk = [&](int c) {
+            if (has_acc) {
+              ptx::tmem_ld_32x32b_x32(tmem_row + sb * sub + c * 32, v);
+              ptx::tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float x = __uint_as_float(v[i]);
+              if (bias_row != nullptr) x += __ldg(bias_row + min(c0 + c * 32 + i, p.cols - 1));
+              if (p.activation != 0) x = element_act(p.activation, x);
+              v[i] = __float_as_uint(x);
+            }
+          };
+#pragma unroll 1
+          for (int c = 0; c < sub / 32; ++c) {
+            load_chunk(c);
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c0 + c * 32 + i < p.cols) amax = fmaxf(amax, fabsf(__uint_as_float(v[i])));
+          }
+          const float scale = amax == 0.f ? 1.0f : amax * (1.0f / 448.0f);
+          const float inv = 1.0f / scale;
+          if (row_ok) p.out_scales[static_cast<size_t>(row) * (p.cols / sub) + c0 / sub] = scale;
+#pragma unroll 1
+          for (int c = 0; c < sub / 32; ++c) {
+            load_chunk(c);
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float q[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) q[e] = fminf(fmaxf(__uint_as_float(v[4 * j + e]) * inv, -448.f), 448.f);
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q[0], q[1]), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q[2], q[3]), __NV_SATFINITE, __NV_E4M3);
+              w[j] = lo | (hi << 16);
+            }
+            const int col = c0 + c * 32;
+            if (row_ok && col < p.cols) {      // cols is a multiple of quant_sub, hence of 32
+              *reinterpret_cast<uint4*>(qrow + col) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(qrow + col + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+          }
         }
         if (has_acc) {
           ptx::tcgen05_fence_before();

@@ -48,7 +48,11 @@ class Config:
     collective  two CTAs of a cluster share one 256-row tile (`cta_group::2`).
     grid_minor_dim / grid_tile_width
                 rasterisation of tiles inside a group (band width along the minor dim).
-    split_k, split_m, persistent, post_scale, epilogue_quant_*
+    epilogue_quant_qtype / epilogue_quant_subchannel_size
+                the forward quantises its result in the epilogue and returns a QArray of
+                float8_e4m3fn values with one float32 scale per row and `subchannel_size`
+                (64, 128 or 256) columns.
+    split_k, split_m, persistent, post_scale
                 kept for schema compatibility; only their defaults are implemented.
   """
 
@@ -70,6 +74,16 @@ class Config:
     if self.block_m % 8:
       raise ValueError("block_m must be a multiple of 8")
 
+  @property
+  def output_quantisation(self) -> int:
+    """Columns per output scale when the epilogue quantises the result, else 0."""
+    if self.epilogue_quant_qtype is None and self.epilogue_quant_subchannel_size is None:
+      return 0
+    name = str(self.epilogue_quant_qtype).replace("torch.", "")
+    if name not in ("float8_e4m3fn", "f8_e4m3fn") or self.epilogue_quant_subchannel_size not in (64, 128, 256):
+      raise NotImplementedError("epilogue quantisation: float8_e4m3fn with 64, 128 or 256 columns per scale")
+    return int(self.epilogue_quant_subchannel_size)
+
   def native(self, max_stages: int = 8) -> tuple:
     """The knobs the kernels actually see; configs with equal `native()` run the same code."""
     stages = max(2, min(max_stages, (self.block_k * self.num_stages) // 64))
@@ -77,11 +91,8 @@ class Config:
             self.grid_tile_width)
 
   def to_capi(self) -> _capi.Config:
-    if (self.split_k != 1 or self.split_m != 1 or self.post_scale
-        or self.epilogue_quant_qtype is not None or self.epilogue_quant_subchannel_size is not None):
-      raise NotImplementedError(
-          "split_k, split_m, post_scale and epilogue quantisation are not implemented by the "
-          "B200 kernels")
+    if self.split_k != 1 or self.split_m != 1 or self.post_scale:
+      raise NotImplementedError("split_k, split_m and post_scale are not implemented by the B200 kernels")
     block_n, stages, collective, minor, width = self.native()
     # The library lowers the depth itself if the ring does not fit in shared memory.
     return _capi.Config(block_m=128, block_n=block_n, block_k=64, num_stages=stages,
@@ -152,6 +163,16 @@ def _as_int32_device(gs, device) -> torch.Tensor:
   if gs.device != device:
     gs = gs.to(device, non_blocking=True)
   return gs.contiguous()
+
+
+def _dequantize_rows(x: QArray) -> torch.Tensor:
+  """bf16 values of a row-quantised matrix: qvalue [M, K] with scale [M, K / sub]."""
+  q, s = x.qvalue, x.scale
+  if q.ndim != 2 or s.ndim != 2 or s.shape[0] != q.shape[0] or q.shape[1] % max(s.shape[1], 1):
+    raise NotImplementedError("quantised lhs: values [M, K] with scales [M, K / subchannel]")
+  sub = q.shape[1] // s.shape[1]
+  return (q.to(torch.float32).reshape(q.shape[0], s.shape[1], sub) * s.to(torch.float32)[:, :, None]
+          ).reshape(q.shape).to(torch.bfloat16)
 
 
 def _normalize_rhs(rhs, rhs_scale):
@@ -241,7 +262,9 @@ class B200RaggedDot(base.RaggedDot):
       raise NotImplementedError("group_offset / zero_initialize=False: default or ragged-contracting "
                                 "dimension numbers only")
     if isinstance(lhs, QArray):
-      raise NotImplementedError("quantised lhs is not supported")
+      # A quantised lhs (the QArray an epilogue-quantising ragged_dot returned: e4m3 values with
+      # one scale per row and block of columns) is expanded to bf16 before the product.
+      lhs = _dequantize_rows(lhs)
     rhs, scale = _normalize_rhs(rhs, rhs_scale)
     if not lhs.is_cuda:
       raise NotImplementedError("B200RaggedDot runs on CUDA tensors only (no CPU fallback)")
@@ -271,6 +294,23 @@ class B200RaggedDot(base.RaggedDot):
     if dims == base.DEFAULT_RAGGED_DOT_DIM_NUMS:
       if lhs.ndim != 2 or rhs.ndim != 3 or lhs.shape[1] != rhs.shape[1]:
         raise ValueError(f"incompatible shapes {tuple(lhs.shape)} and {tuple(rhs.shape)}")
+      quant_sub = config.output_quantisation if config is not None else 0
+      if quant_sub:
+        if (scale is not None or windowed or return_residuals or lhs.dtype != rhs.dtype
+            or fuse_gateup_activation is not None):
+          raise NotImplementedError("epilogue quantisation: plain 16-bit forward without residuals")
+        n = rhs.shape[2]
+        if n % quant_sub:
+          raise NotImplementedError("epilogue quantisation needs N to be a multiple of the subchannel size")
+        act = fusable_activation(activation)
+        if activation is not None and act is None:
+          raise NotImplementedError("epilogue quantisation fuses only the recognised activations")
+        q = torch.empty((lhs.shape[0], n), dtype=torch.float8_e4m3fn, device=lhs.device)
+        qs = torch.empty((lhs.shape[0], n // quant_sub), dtype=torch.float32, device=lhs.device)
+        if ccfg.block_n % quant_sub:
+          ccfg.block_n = 256
+        _capi.ragged_dot_fwd_quant_out(lhs, rhs, gs, q, qs, quant_sub, element_activation=act, config=ccfg)
+        return QArray(q, qs), None
       # `activation` on the float32 accumulator inside the kernel (api.py:108-113 upstream), for
       # the callables the epilogue knows; never when the residuals (the result before the
       # activation) are asked for, and only on the plain 16-bit forward.
