@@ -346,7 +346,7 @@ EP_TOKENS, EP_K, EP_N, EP_G, EP_TOPK = 8192, 7168, 2048, 256, 8
 
 def ep_config(world: int, exchange: str, chunks: int) -> dict:
   """The `config` object of the line: identical in the GPU arm and the reference arm."""
-  return {"workload": "ep",
+  return {"workload": "ep" if (EP_TOKENS, EP_G) == (8192, 256) else f"ep[{EP_TOKENS} tokens, {EP_G} experts]",
           "note": "expert-parallel MoE layer: route, dispatch rows to the experts' owners, grouped GEMM, "
                   "return rows, gate-weighted combine",
           "tokens_per_rank": EP_TOKENS, "k": EP_K, "n": EP_N, "experts": EP_G, "top_k": EP_TOPK,
@@ -640,13 +640,15 @@ def main():
                   help="weight type of a single-kernel run (cfg3 defaults to fp8)")
   ap.add_argument("--groups", type=int, default=0,
                   help="keep only the first N groups of the workload (smaller profiler captures)")
-  ap.add_argument("--ep-exchange", default=None, choices=[None, "fused", "p2p", "nccl"],
+  ap.add_argument("--ep-exchange", default=None, choices=[None, "fused", "nccl"],
                   help="row exchange of the expert-parallel layer (default: the fused kernel)")
   ap.add_argument("--ep-chunks", type=int, default=0,
                   help="expert chunks of the p2p / nccl exchanges whose transfers overlap the neighbouring GEMMs")
   ap.add_argument("--kernel-only", action="store_true",
                   help="exactly --steps launches of the timed region, no padding for the clock sampler")
   ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel suite of the N = 1 line")
+  ap.add_argument("--ep-tokens", type=int, default=0, help="tokens per rank of the ep workload (profiler captures)")
+  ap.add_argument("--ep-experts", type=int, default=0, help="experts of the ep workload (profiler captures)")
   args = ap.parse_args()
 
   world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -655,6 +657,11 @@ def main():
   from tokamax_b200.ragged_dot import arg_specs
 
   workload = args.workload or "ep"
+  global EP_TOKENS, EP_G
+  if args.ep_tokens:
+    EP_TOKENS = args.ep_tokens
+  if args.ep_experts:
+    EP_G = args.ep_experts
   if args.impl == "reference":
     line = run_reference_arm(args, world, rank)
     if line is not None:

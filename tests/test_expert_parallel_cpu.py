@@ -165,3 +165,67 @@ def test_expert_parallel_backward_matches_autograd(world):
     assert p.exitcode == 0
   for rank, e_tok, e_rhs, e_gates in results:
     assert e_tok < 3e-2 and e_rhs < 3e-2 and e_gates < 3e-2, (rank, e_tok, e_rhs, e_gates)
+
+
+# ---------------------------------------------------------------- host-side fault injection
+class _CorruptCounts(OracleBackend):
+  """A rank whose sort reports wrong per-expert counts: `phantom` announces rows it does not
+  have, `dropped` forgets rows it has, `negative` reports a negative count."""
+
+  def __init__(self, kind):
+    self.kind = kind
+
+  def sort_pairs(self, expert_ids, num_experts):
+    pos, counts = super().sort_pairs(expert_ids, num_experts)
+    counts = counts.clone()
+    e = int(torch.nonzero(counts)[0])
+    if self.kind == "phantom":
+      counts[e] += 5
+    elif self.kind == "dropped":
+      counts[e] -= 1
+    else:
+      counts[e] = -counts[e]
+    return pos, counts
+
+
+def _fault_worker(rank, world, port, q, kind, chunks):
+  os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+  dist.init_process_group("gloo", rank=rank, world_size=world)
+  try:
+    from tokamax_b200.expert_parallel import ExpertParallelMoE
+    rhs, per_rank = _inputs(world)
+    gl = G // world
+    backend = _CorruptCounts(kind) if rank == 1 else OracleBackend()
+    layer = ExpertParallelMoE(rhs[rank * gl:(rank + 1) * gl], G, backend=backend, num_chunks=chunks)
+    tok, ids, gates = per_rank[rank]
+    try:
+      layer(tok, ids, gates)
+      q.put((rank, "no error"))
+    except RuntimeError as e:
+      q.put((rank, str(e)))
+    # the group is still usable: the same layer with honest counts runs afterwards
+    layer2 = ExpertParallelMoE(rhs[rank * gl:(rank + 1) * gl], G, backend=OracleBackend(), num_chunks=chunks)
+    y, _ = layer2(tok, ids, gates)
+    q.put((rank, float((y.float() - _dense_moe(tok, ids, gates, rhs)).abs().max())))
+  finally:
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("kind,chunks", [("phantom", 1), ("dropped", 1), ("negative", 2)])
+def test_corrupt_counts_are_refused_on_every_rank(kind, chunks):
+  """Failure made on the host: one rank's counts are wrong.  Every rank raises before any row
+  is exchanged (no rank is left waiting in a collective), and the next step works."""
+  ctx = mp.get_context("spawn")
+  q = ctx.Queue()
+  port = _free_port()
+  procs = [ctx.Process(target=_fault_worker, args=(r, 2, port, q, kind, chunks)) for r in range(2)]
+  for p in procs:
+    p.start()
+  results = [q.get(timeout=120) for _ in range(4)]
+  for p in procs:
+    p.join(timeout=60)
+    assert p.exitcode == 0
+  msgs = [r for r in results if isinstance(r[1], str)]
+  errs = [r for r in results if not isinstance(r[1], str)]
+  assert len(msgs) == 2 and all("inconsistent per-expert counts" in m for _, m in msgs), msgs
+  assert len(errs) == 2 and all(e < 2e-2 for _, e in errs), errs

@@ -196,6 +196,24 @@ class ExpertParallelMoE:
                               if self.group is not None else peer, self.group))
     return dist.batch_isend_irecv(ops) if ops else []
 
+  def _check_counts(self, sent: torch.Tensor, received: torch.Tensor, num_pairs: int) -> None:
+    """Refuses a step whose exchanged counts cannot be right, on every rank at once (the
+    verdict is all-reduced, so no rank walks into a row exchange the others have left):
+    a negative count, a total that differs from this rank's number of routed pairs (rows
+    dropped or invented by the sort), or rows announced as sent that nobody announces as received.  `sent` / `received` are host int tensors
+    [W, G/W] (what this rank sends to / receives from each rank, per local expert)."""
+    bad = int(sent.min()) < 0 or int(received.min()) < 0 or int(sent.sum()) != num_pairs
+    totals = torch.tensor([int(sent.sum()), int(received.sum()), 1 if bad else 0], dtype=torch.int64)
+    if self.world > 1:
+      totals = totals.to(self.rhs_local.device)
+      dist.all_reduce(totals, group=self.group)
+      totals = totals.cpu()
+    if int(totals[2]) != 0 or int(totals[0]) != int(totals[1]):
+      raise RuntimeError(
+          "expert-parallel dispatch: inconsistent per-expert counts across ranks "
+          f"(rows announced as sent {int(totals[0])}, as received {int(totals[1])}, "
+          f"ranks with invalid counts {int(totals[2])}); the step was not run")
+
   def dispatch(self, tokens: torch.Tensor, expert_ids: torch.Tensor):
     """Returns (rows [R, K] in (source rank, local expert) order, DispatchPlan)."""
     t, top_k = expert_ids.shape
@@ -204,9 +222,11 @@ class ExpertParallelMoE:
     counts = counts.reshape(w, gl)                         # [dest rank, expert]
     recv_counts = torch.empty_like(counts)                 # [source rank, expert]
     self._all_to_all(recv_counts, counts, None, None)
-    host = torch.stack([counts.sum(1), recv_counts.sum(1)]).cpu()   # the one host read
-    send_splits = [int(v) for v in host[0]]
-    recv_splits = [int(v) for v in host[1]]
+    valid = ((expert_ids >= 0) & (expert_ids < self.num_experts)).sum().reshape(1, 1).expand(1, gl).to(counts.dtype)
+    host_counts = torch.cat([counts, recv_counts, valid]).cpu()     # the one host read
+    self._check_counts(host_counts[:w], host_counts[w:2 * w], int(host_counts[2 * w, 0]))
+    send_splits = [int(v) for v in host_counts[:w].sum(1)]
+    recv_splits = [int(v) for v in host_counts[w:2 * w].sum(1)]
     packed = self.backend.gather_rows(tokens, pos, top_k)  # expert order == (dest rank, expert)
     if w == 1:
       recv = packed
@@ -335,7 +355,10 @@ class ExpertParallelMoE:
     counts = counts.reshape(w, gl)
     recv_counts = torch.empty_like(counts)
     self._all_to_all(recv_counts, counts, None, None)
-    host = torch.stack([counts, recv_counts]).cpu()                 # the one host read
+    valid = ((expert_ids >= 0) & (expert_ids < self.num_experts)).sum().reshape(1, 1).expand(1, gl).to(counts.dtype)
+    host_all = torch.cat([counts, recv_counts, valid]).cpu()        # the one host read
+    host = torch.stack([host_all[:w], host_all[w:2 * w]])
+    self._check_counts(host[0], host[1], int(host_all[2 * w, 0]))
     send_c = host[0].reshape(w, chunks, ce).sum(2)                   # [dest, chunk] rows
     recv_c = host[1].reshape(w, chunks, ce).sum(2)                   # [src, chunk] rows
     send_off = (host[0].reshape(-1).cumsum(0) - host[0].reshape(-1)).reshape(w, gl)  # packed-row offsets
