@@ -284,7 +284,11 @@ TKMX_API int tkmx_moe_sort_pairs(const int32_t* expert_ids, int64_t num_pairs, i
  *     TKMX_ERR_TOO_LARGE, with the reason in tkmx_last_cuda_error(), and enqueues nothing.
  *   - The call allocates nothing (no cudaMalloc / cudaFree, no allocating library routine).
  *   - The first call on each device looks up the array's device address (with that device
- *     current); make that first call before starting any stream capture.
+ *     current); make that first call before starting any stream capture.  If it is also the
+ *     process's first use of this library on that device, it is when the CUDA runtime loads
+ *     the library image -- and with it this array and the library's other static device
+ *     arrays -- into device memory: a host that is about to claim all remaining device memory
+ *     for its own arena must make that first call before it does.
  *   - All calls on a device share the one array, which keeps whatever the previous call left
  *     in it.  Nothing in it has to start at zero: every entry a call reads was written by that
  *     same call first.  Two calls that may overlap on the GPU (different streams) race on it;
@@ -320,7 +324,8 @@ TKMX_API int tkmx_moe_sort_pairs_inverse(const int32_t* expert_ids, int64_t num_
  *
  * Buffers every rank allocates in memory its peers can address, with the same sizes everywhere:
  *   recv     [capacity_rows, k]  token rows this rank's experts receive, (local expert, source) order
- *   arrive   uint32[G/W]         rows arrived per local expert
+ *   arrive   uint32[G/W + 1]     rows arrived per local expert; the last word is this rank's
+ *                                multiplication progress, on which its senders pace themselves
  *   ret      [T * top_k, n]      this rank's pairs' output rows in expert-sorted order
  *   counts   int32[W, G]         every rank's per-expert pair counts
  *   flags    uint32[W]           barrier flags, zero before the first call

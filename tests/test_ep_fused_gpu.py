@@ -52,7 +52,7 @@ class VirtualRanks:
     self.w, self.g, self.gl, self.pairs, self.cap = w, g, g // w, t * top_k, w * t * top_k
     mk = lambda shape, dt: [torch.zeros(shape, dtype=dt, device=dev) for _ in range(w)]
     self.recv = mk((self.cap, k), dtype)
-    self.arrive = mk((self.gl,), torch.int32)
+    self.arrive = mk((self.gl + 1,), torch.int32)
     self.ret = mk((self.pairs, n), dtype)
     self.counts = mk((w, g), torch.int32)
     self.flags = mk((w,), torch.int32)
@@ -158,7 +158,7 @@ def _run_virtual(capi, w, t, k, n, g, top_k, pair, seed, bad_ids=False, dtype=to
   for r in range(w):
     got = vr.plan[r][:gl].cpu().numpy()
     assert np.array_equal(got, hist[r * gl:(r + 1) * gl]), f"rank {r}: group sizes"
-    assert np.array_equal(vr.arrive[r].cpu().numpy(), got), f"rank {r}: arrival counters"
+    assert np.array_equal(vr.arrive[r][:gl].cpu().numpy(), got), f"rank {r}: arrival counters"
   for r in range(w):
     want = _dense_moe(toks[r], idss[r], gatess[r], rhs)
     helpers.assert_close(ys[r], want.to(dtype), what=f"virtual rank {r} of {w}")

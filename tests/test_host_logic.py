@@ -328,3 +328,26 @@ def test_cache_wire_format_is_the_references():
   from tokamax_b200.ragged_dot import base as base_lib
   assert op.bind(a, d, group_sizes=g2, ragged_dot_dimension_numbers=base_lib.RAGGED_CONTRACTING_DOT_DIM_NUMS
                  ).autotuning_cache_key == ba_drhs.autotuning_cache_key
+
+
+def test_xla_ffi_shim_type_checks_against_the_c_abi():
+  """The JAX-facing handlers (csrc/xla_ffi_shim.cc) need jaxlib's headers to build, which do
+  not exist here; a test double of `xla/ffi/api/ffi.h` (tests/ffi_stub) lets the compiler check
+  every call the handlers make into include/tokamax_b200.h (argument count, order and types),
+  and the attribute names are compared with the binding shown in INTEGRATION.md."""
+  import re
+  import subprocess
+  shim = os.path.join(ROOT, "tokamax_b200", "csrc", "xla_ffi_shim.cc")
+  proc = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-Wall", "-Werror",
+                         "-I" + os.path.join(ROOT, "tests", "ffi_stub"), "-I/usr/local/cuda/include", shim],
+                        capture_output=True, text=True)
+  assert proc.returncode == 0, proc.stderr
+  src = open(shim).read()
+  attrs = set(re.findall(r'Attr<int32_t>\("(\w+)"\)', src))
+  assert attrs == {"rhs_layout", "activation", "block_n", "num_stages", "collective", "grid_minor_dim",
+                   "grid_tile_width"}
+  doc = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+  for name in attrs:
+    assert name in doc, f"attribute {name} of the FFI handlers is not in INTEGRATION.md's binding"
+  for sym in re.findall(r"XLA_FFI_DEFINE_HANDLER_SYMBOL\((\w+),", src):
+    assert sym in doc, f"handler {sym} is not named in INTEGRATION.md"

@@ -32,10 +32,19 @@ def test_static_scratch_sort_matches_workspace_sort_twice_in_a_row():
     want_pos, want_counts = _capi.moe_sort_pairs(ids, num_experts)
     pos = torch.full((num_pairs,), -7, dtype=torch.int32, device="cuda")
     counts = torch.full((num_experts,), -7, dtype=torch.int32, device="cuda")
-    before = torch.cuda.memory_allocated()
+    # Warm-up call: the first call on a device looks up the scratch array's address (and, in a
+    # fresh process, is when CUDA loads the library image onto the device).
     _capi.moe_sort_pairs_static(ids, num_experts, pos, counts)
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before      # nothing was taken from torch's pool either
+    pos.fill_(-7)
+    counts.fill_(-7)
+    before = torch.cuda.memory_allocated()
+    free_before, _ = torch.cuda.mem_get_info()
+    _capi.moe_sort_pairs_static(ids, num_experts, pos, counts)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert torch.cuda.memory_allocated() == before      # nothing was taken from torch's pool
+    assert free_after >= free_before                    # ... and nothing from the device behind its back
     assert torch.equal(pos, want_pos)
     assert torch.equal(counts, want_counts)
     # immediately again, same inputs: identical

@@ -184,7 +184,7 @@ ep_exchange_plan_kernel(const EpExchangeParams x) {
   if (tid == 0) s_abort = 0;
   // 0. what the peers add to during this step starts at zero; they can only start adding
   //    after they have seen this rank's flag below.
-  for (int i = tid; i < gl; i += blockDim.x) x.arrive[i] = 0u;
+  for (int i = tid; i <= gl; i += blockDim.x) x.arrive[i] = 0u;    // [gl] is the multiplication progress word
   // 1. this rank's counts into row `rank` of every rank's matrix
   for (int idx = tid; idx < W * G; idx += blockDim.x) {
     const int peer = idx / G, e = idx - peer * G;
@@ -266,6 +266,8 @@ struct EpFusedParams {
   const int32_t* plan;           // EpPlanLayout tables of this step
   const uint64_t* peer_tab;      // device, see EpTab
   const uint32_t* arrive;        // local arrival counters [G/W]
+  uint32_t* progress;            // local word (arrive[G/W]): 1 + furthest local expert whose tiles have been started
+  int32_t ahead_rows;            // senders stay at most this many receive-buffer rows ahead of `progress` (0: no pacing)
   int32_t world, rank, top_k;
   int32_t num_experts;           // global G
   int32_t row_vec;               // 16-byte pieces per token row
@@ -276,8 +278,8 @@ struct EpFusedParams {
 
 // Sending side, one warp: rows in send order (local expert major, then owner), kEpItemRows at a
 // time, so that every owner receives its first experts first.
-__device__ __forceinline__ void ep_send_rows(const EpFusedParams& ep, const int* s_vstart, int sender,
-                                             int num_senders, int lane, int32_t* status) {
+__device__ __forceinline__ void ep_send_rows(const EpFusedParams& ep, const int* s_vstart, const int* s_need,
+                                             int sender, int num_senders, int lane, int32_t* status) {
   const int G = ep.num_experts, W = ep.world;
   const EpPlanLayout L = ep_plan_layout(G, W);
   const int P = s_vstart[G];
@@ -309,6 +311,25 @@ __device__ __forceinline__ void ep_send_rows(const EpFusedParams& ep, const int*
       }
     }
     const int nrows = min(kEpItemRows, P - item * kEpItemRows);
+    if (s_need != nullptr) {
+      // Pacing: the item's last row belongs to its furthest expert (rows are sent expert-major).
+      const int le_last = __shfl_sync(0xffffffffu, v / W, nrows - 1);
+      if (lane == 0) {
+        const uint32_t need = static_cast<uint32_t>(s_need[le_last]);
+        if (need > 0u && *reinterpret_cast<volatile uint32_t*>(ep.progress) < need) {
+          const uint64_t t0 = ptx::gtimer_ns();
+          uint32_t spins = 0;
+          while (*reinterpret_cast<volatile uint32_t*>(ep.progress) < need) {
+            __nanosleep(200);
+            if ((++spins & 0xFFu) == 0 && ptx::gtimer_ns() - t0 > 2000000000ull) {
+              atomicCAS(status, 0, kDevTimeoutArrival);   // give up pacing, never the rows
+              break;
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
     for (int j = 0; j < nrows; ++j) {
       const uint4* s4 = reinterpret_cast<const uint4*>(shfl64(src, j));
       uint4* d4 = reinterpret_cast<uint4*>(shfl64(dst, j));

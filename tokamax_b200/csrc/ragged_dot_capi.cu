@@ -1286,6 +1286,7 @@ int tkmx_ep_moe_fused(const void* tokens, const int32_t* sorted_pair, const void
   assign_sched(*dev, &p, true);
   p.swap_rows = rc.pair ? env_int("TKMX_SWAP_ROWS", 192, 0, 192) : 0;
   p.balance_tiles = env_int("TKMX_BALANCE_TILES", 0, 0, 1);
+  p.prefetch_blocks = env_int("TKMX_EP_PREFETCH", 0, 0, 64);
 
   tkmx::EpFusedParams ep = {};
   ep.tokens = tokens;
@@ -1301,6 +1302,11 @@ int tkmx_ep_moe_fused(const void* tokens, const int32_t* sorted_pair, const void
   ep.ret_row_bytes = int32_t(n * 2);
   ep.capacity_rows = int32_t(capacity_rows);
   ep.phases = phases;
+  ep.progress = const_cast<uint32_t*>(arrive_local) + gl;
+  // Senders stay at most this much of the receive buffer ahead of the multiplication (rows sent
+  // earlier than that have left L2 by the time they are multiplied).  TKMX_EP_AHEAD_MB = 0: no pacing.
+  ep.ahead_rows = int32_t(std::min<int64_t>(int64_t(env_int("TKMX_EP_AHEAD_MB", 0, 0, 4096)) * (1 << 20) / (k * 2),
+                                            int64_t(1) << 30));
 
   // Every SM takes part (its two sender warps do, even when it draws no tile).
   int grid = dev->num_sms;

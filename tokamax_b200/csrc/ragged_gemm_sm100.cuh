@@ -138,6 +138,7 @@ struct SmemLayout {
   uint32_t row_start;   // int32[G + 1]
   uint32_t tile_start;  // int32[G + 1]  (rows modes only)
   uint32_t ep_vstart;   // int32[ep_experts + 1]: send-order prefix sums of the expert-parallel form
+  uint32_t ep_need;     // int32[G]: multiplication progress a sender waits for before it sends an expert's rows
   uint32_t total;
 };
 
@@ -164,6 +165,8 @@ __host__ __device__ inline SmemLayout make_smem_layout(int block_n, bool pair, i
   if (need_tile_start) off += 4u * (num_groups + 1);
   l.ep_vstart = off;
   if (ep_experts > 0) off += 4u * (ep_experts + 1);
+  l.ep_need = off;
+  if (ep_experts > 0) off += 4u * (num_groups + 1);
   l.total = off;
   return l;
 }
@@ -642,6 +645,7 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   int* row_start = reinterpret_cast<int*>(base_ptr + L.row_start);
   int* tile_start = reinterpret_cast<int*>(base_ptr + L.tile_start);
   int* ep_vstart = reinterpret_cast<int*>(base_ptr + L.ep_vstart);
+  int* ep_need = reinterpret_cast<int*>(base_ptr + L.ep_need);
   const bool ep_multiply = !kEp || (ep.phases & 2) != 0;   // false: this launch only sends rows
 
   const int warp = threadIdx.x >> 5;
@@ -746,6 +750,20 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   }
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if constexpr (kEp) {
+    // Pacing of the senders: rows written long before they are multiplied fall out of L2 and
+    // are read back from HBM, so an expert's rows are sent only once the multiplication has
+    // come within `ahead_rows` rows of it.  ep_need[e] = the progress value (1 + index of the
+    // furthest expert whose tiles have been started) at which expert e may be sent.
+    if (warp == 3 && lane == 0) {
+      int e0 = 0;
+      for (int e = 0; e < p.num_groups; ++e) {
+        while (e0 < e && row_start[e] - row_start[e0] > ep.ahead_rows) ++e0;
+        ep_need[e] = ep.ahead_rows > 0 ? e0 : 0;
+      }
+    }
+    __syncthreads();
+  }
 
   // ------------------------------------------------------------------ roles
   if (warp == 0) {
@@ -834,6 +852,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                     ? p.cols / 2 - kBlockN / 2 : 0;  // extra offset of the up chunks
         const int slab = (kMode != kContract && t.group >= 0) ? t.group % p.rhs_groups : 0;
         if constexpr (kEp) {
+          if (cta_rank == 0 && t.group >= 0 && t.group != ep_ready_group)
+            atomicMax(ep.progress, static_cast<uint32_t>(t.group) + 1u);   // what the senders pace themselves on
           // The tile's rows come from every rank: wait until the expert's arrival counter has
           // reached its row count (tiles are visited in expert order, as the rows are sent).
           if (t.group >= 0 && t.group != ep_ready_group) {
@@ -911,6 +931,13 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
                 for (int j = 0; j < kLocalN / 64; ++j)
                   ptx::tma_load_3d_pair(sb + j * kChunkBytes, &map_b, col0 + 64 * j, kb * kBlockK, slab, full);
+                // Weights that are used by one tile only come from HBM: ask L2 for the blocks
+                // beyond the shared-memory ring, so more bytes are in flight than the ring holds.
+                if (p.prefetch_blocks > 0 && kb + p.prefetch_blocks < t.num_kb) {
+#pragma unroll
+                  for (int j = 0; j < kLocalN / 64; ++j)
+                    ptx::tma_prefetch_l2_3d(&map_b, col0 + 64 * j, (kb + p.prefetch_blocks) * kBlockK, slab);
+                }
               } else {
                 ptx::tma_load_3d_pair(sb, &map_b, kb * kBlockK, col0, slab, full);
               }
@@ -1008,7 +1035,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       // Consecutive items go to different CTAs, so every SM's links carry every expert. =====
       const int local = warp < 8 ? warp - 2 : warp - 6;
       if (ep.phases & 1)
-        ep_send_rows(ep, ep_vstart, local * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x),
+        ep_send_rows(ep, ep_vstart, (ep.phases & 2) ? ep_need : nullptr,
+                     local * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x),
                      kEpSendWarps * static_cast<int>(gridDim.x), lane, p.status);
     }
     if (kMode == kContract && warp == 2) {

@@ -6,9 +6,8 @@
 // Needs jaxlib's header tree (`xla/ffi/api/ffi.h`, found via `jax.ffi.include_dir()`);
 // it is therefore NOT part of libtokamax_b200.so and is compiled only where jaxlib is
 // installed:
-//   g++ -std=c++17 -shared -fPIC -I$(python -c "import jax; print(jax.ffi.include_dir())") \
-//       -I/usr/local/cuda/include xla_ffi_shim.cc -L../lib -ltokamax_b200 \
-//       -o ../lib/libtokamax_b200_ffi.so
+//   g++ -std=c++17 -shared -fPIC -I<jax.ffi.include_dir()> -I/usr/local/cuda/include
+//       xla_ffi_shim.cc -L../lib -ltokamax_b200 -o ../lib/libtokamax_b200_ffi.so
 //
 // Handler contract: buffers are XLA-owned device pointers (never retained), the stream
 // comes from XLA, the handler only enqueues (no synchronisation, no host read of
@@ -16,6 +15,7 @@
 #include <cuda_runtime_api.h>
 
 #include <cstdint>
+#include <initializer_list>
 #include <string>
 
 #include "../../include/tokamax_b200.h"
@@ -46,6 +46,18 @@ ffi::Error ToError(int status, const char* what) {
   return ffi::Error::Internal(msg);
 }
 
+// A result (or operand) buffer must have exactly the shape the kernel is about to write:
+// XLA owns the memory, and a mismatched ffi_call result spec would otherwise be overrun.
+template <typename Buf>
+bool HasShape(const Buf& buf, std::initializer_list<int64_t> want) {
+  auto d = buf.dimensions();
+  if (d.size() != want.size()) return false;
+  size_t i = 0;
+  for (int64_t w : want)
+    if (d[i++] != w) return false;
+  return true;
+}
+
 tkmx_config MakeConfig(int32_t block_n, int32_t num_stages, int32_t collective,
                        int32_t grid_minor_dim, int32_t grid_tile_width) {
   tkmx_config c = {};
@@ -73,6 +85,7 @@ ffi::Error FwdImpl(cudaStream_t stream, ffi::AnyBuffer lhs, ffi::AnyBuffer rhs,
   const int64_t rk = rhs_layout == TKMX_RHS_GKN ? rd[1] : rd[2];
   if (rk != k || group_sizes.dimensions()[0] != g)
     return ffi::Error::InvalidArgument("ragged_dot fwd: contraction / group dimensions do not match");
+  if (!HasShape(*out, {m, n})) return ffi::Error::InvalidArgument("ragged_dot fwd: out must be [m, n]");
   tkmx_config cfg = MakeConfig(block_n, num_stages, collective, grid_minor_dim, grid_tile_width);
   int st = tkmx_ragged_dot_fwd(lhs.untyped_data(), rhs.untyped_data(), group_sizes.typed_data(),
                                /*rhs_scale=*/nullptr, out->untyped_data(), /*workspace=*/nullptr, 0, m,
@@ -94,8 +107,10 @@ ffi::Error FwdQuantImpl(cudaStream_t stream, ffi::AnyBuffer lhs, ffi::AnyBuffer 
   auto rd = rhs.dimensions();
   if (ld.size() != 2 || rd.size() != 3 || rd[1] != ld[1] || group_sizes.dimensions()[0] != rd[0])
     return ffi::Error::InvalidArgument("ragged_dot quantised fwd: expected lhs[m,k], rhs[g,k,n], group_sizes[g]");
-  if (rhs_scale.element_count() != static_cast<size_t>(rd[0] * rd[2]))
-    return ffi::Error::InvalidArgument("ragged_dot quantised fwd: rhs_scale must hold g * n values");
+  if (!HasShape(rhs_scale, {rd[0], rd[2]}) && !HasShape(rhs_scale, {rd[0], 1, rd[2]}))
+    return ffi::Error::InvalidArgument("ragged_dot quantised fwd: rhs_scale must be [g, n] or [g, 1, n]");
+  if (!HasShape(*out, {ld[0], rd[2]}))
+    return ffi::Error::InvalidArgument("ragged_dot quantised fwd: out must be [m, n]");
   tkmx_config cfg = MakeConfig(block_n, num_stages, collective, grid_minor_dim, grid_tile_width);
   int st = tkmx_ragged_dot_fwd(lhs.untyped_data(), rhs.untyped_data(), group_sizes.typed_data(),
                                rhs_scale.typed_data(), out->untyped_data(), workspace->untyped_data(),
@@ -114,6 +129,8 @@ ffi::Error FwdGateUpImpl(cudaStream_t stream, ffi::AnyBuffer lhs, ffi::AnyBuffer
   auto rd = rhs.dimensions();
   if (ld.size() != 2 || rd.size() != 3 || rd[1] != ld[1] || group_sizes.dimensions()[0] != rd[0])
     return ffi::Error::InvalidArgument("ragged_dot gate/up fwd: expected lhs[m,k], rhs[g,k,n], group_sizes[g]");
+  if (rd[2] % 2 != 0 || !HasShape(*out, {ld[0], rd[2] / 2}))
+    return ffi::Error::InvalidArgument("ragged_dot gate/up fwd: out must be [m, n / 2]");
   tkmx_config cfg = MakeConfig(block_n, num_stages, collective, grid_minor_dim, grid_tile_width);
   int st = tkmx_ragged_dot_fwd_gateup(lhs.untyped_data(), rhs.untyped_data(), group_sizes.typed_data(),
                                       out->untyped_data(), ld[0], ld[1], rd[2], rd[0],
@@ -129,8 +146,9 @@ ffi::Error DlhsImpl(cudaStream_t stream, ffi::AnyBuffer dout, ffi::AnyBuffer rhs
                     int32_t grid_tile_width) {
   auto dd = dout.dimensions();
   auto rd = rhs.dimensions();
-  if (dd.size() != 2 || rd.size() != 3 || rd[2] != dd[1])
-    return ffi::Error::InvalidArgument("ragged_dot dlhs: expected dout[m,n], rhs[g,k,n]");
+  if (dd.size() != 2 || rd.size() != 3 || rd[2] != dd[1] || !HasShape(group_sizes, {rd[0]}))
+    return ffi::Error::InvalidArgument("ragged_dot dlhs: expected dout[m,n], rhs[g,k,n], group_sizes[g]");
+  if (!HasShape(*dlhs, {dd[0], rd[1]})) return ffi::Error::InvalidArgument("ragged_dot dlhs: dlhs must be [m, k]");
   tkmx_config cfg = MakeConfig(block_n, num_stages, collective, grid_minor_dim, grid_tile_width);
   int st = tkmx_ragged_dot_dlhs(dout.untyped_data(), rhs.untyped_data(), group_sizes.typed_data(),
                                 dlhs->untyped_data(), nullptr, 0, dd[0], rd[1], rd[2], rd[0],
@@ -148,7 +166,10 @@ ffi::Error DrhsImpl(cudaStream_t stream, ffi::AnyBuffer lhs, ffi::AnyBuffer dout
   auto dd = dout.dimensions();
   if (ld.size() != 2 || dd.size() != 2 || ld[0] != dd[0])
     return ffi::Error::InvalidArgument("ragged_dot drhs: expected lhs[m,k], dout[m,n]");
+  if (group_sizes.dimensions().size() != 1)
+    return ffi::Error::InvalidArgument("ragged_dot drhs: group_sizes must be [g]");
   const int64_t g = group_sizes.dimensions()[0];
+  if (!HasShape(*drhs, {g, ld[1], dd[1]})) return ffi::Error::InvalidArgument("ragged_dot drhs: drhs must be [g, k, n]");
   tkmx_config cfg = MakeConfig(block_n, num_stages, collective, grid_minor_dim, grid_tile_width);
   int st = tkmx_ragged_dot_drhs(lhs.untyped_data(), dout.untyped_data(), group_sizes.typed_data(),
                                 drhs->untyped_data(), nullptr, 0, ld[0], ld[1], dd[1], g,
