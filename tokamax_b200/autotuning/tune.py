@@ -1,6 +1,11 @@
 """Autotunes named ragged-dot workloads on the current GPU and writes the cache file.
 
   python -m tokamax_b200.autotuning.tune --workloads cfg2,cfg4,dsv3 --ops fwd,dlhs,drhs
+  python -m tokamax_b200.autotuning.tune --workloads memory_bound,mixtral/8x7b --ops fwd
+
+A workload is one of the headline configurations (cfg1 ... dsv3) or the full name of one of the
+reference's benchmark specs (`arg_specs.ARG_SPECS`: "compute_bound", "memory_bound",
+"mixtral/8x7b", "maxtext/deepseek-v3-...").
 
 For every (workload, contraction) the op's search space is timed (configs that map onto the
 same kernel parameters are timed once) and the best few entries are merged into
@@ -52,6 +57,16 @@ def bound_arguments(op: b200.B200RaggedDot, w: arg_specs.Workload, which: str, d
   return op.bind(lhs, rhs, group_sizes=gs)
 
 
+def named_workload(name: str) -> arg_specs.Workload:
+  """A headline configuration, or one of the reference's benchmark specs as a Workload."""
+  if name in arg_specs.NAMED_ARG_SPECS:
+    a = arg_specs.NAMED_ARG_SPECS[name].args
+    (m, k), (g, _, n) = a["lhs"].shape, a["rhs"].shape
+    return arg_specs.Workload(name, m, k, n, g, tuple(a["group_sizes"].representative_value),
+                              rhs_dtype=a["rhs"].dtype)
+  return arg_specs.workload(name)
+
+
 def main(argv=None):
   ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
   ap.add_argument("--workloads", default="cfg2,cfg4")
@@ -73,7 +88,7 @@ def main(argv=None):
     merged = {}
   tuner = autotuner_lib.Autotuner(iterations=args.iterations, warmup=2)
   for name in args.workloads.split(","):
-    w = arg_specs.workload(name)
+    w = named_workload(name)
     for which in args.ops.split(","):
       if which != "fwd" and w.rhs_dtype != torch.bfloat16:
         continue
