@@ -56,6 +56,9 @@ UNIT = "TFLOP/s"
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures,
 # by kernel-suite entry name; None where no capture exists.
 NCU_TRAFFIC_BYTES = {"cfg2.fwd": 2.643e9}
+# The fused expert-parallel kernel on one rank: 2.74 GB captured on a quarter-size case (2048
+# tokens, 64 experts); rows and weights both scale by 4 to the full workload, traffic with them.
+NCU_TRAFFIC_EP_QUARTER = 2.74e9
 
 
 # ----------------------------------------------------------------------------- utilities
@@ -77,12 +80,23 @@ class ClockSampler:
             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
             "clocks_event_reasons.sw_power_cap")
 
-  def __init__(self, gpu_id: str):
-    self.gpu_id = gpu_id
+  def __init__(self, gpu_id: str | None):
+    self.gpu_id = gpu_id          # None: sample nothing (ranks whose line is not printed)
     self.proc = None
     self.lines: list[str] = []
+    self.first = 0
+
+  def wait_ready(self, timeout_s: float = 8.0):
+    """Blocks until the tool has printed its first sample (its start-up takes a second or more
+    on a box with many GPUs), then drops what it saw so far: those samples are of an idle GPU."""
+    t_end = time.time() + timeout_s
+    while self.proc is not None and not self.lines and time.time() < t_end:
+      time.sleep(0.02)
+    self.first = len(self.lines)
 
   def __enter__(self):
+    if self.gpu_id is None:
+      return self
     try:
       self.proc = subprocess.Popen(
           ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -110,7 +124,7 @@ class ClockSampler:
     sm, mx = [], []
     reasons = set()
     names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-    for line in self.lines:
+    for line in self.lines[self.first:]:
       parts = [p.strip() for p in line.split(",")]
       if len(parts) < 6:
         continue
@@ -499,7 +513,7 @@ def run_expert_parallel(args, peaks, world, rank, local_rank):
   layer = ExpertParallelMoE(rhs, EP_G, num_chunks=args.ep_chunks if args.ep_chunks > 0 else 4,
                             exchange=args.ep_exchange)
   stream = torch.cuda.current_stream()
-  sampler_id = gpu_id_for_smi(local_rank)
+  sampler_id = gpu_id_for_smi(local_rank) if rank == 0 else None   # rank 0 prints the line
 
   def barrier():
     if world > 1:
@@ -513,6 +527,9 @@ def run_expert_parallel(args, peaks, world, rank, local_rank):
   layer.gemm_events = []          # (start, end) CUDA events around the grouped-GEMM launch of each step
   with ClockSampler(sampler_id) as clocks:
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    clocks.wait_ready()
+    for _ in range(3):              # the GPU is busy again when the first kept sample is taken
+      layer(tokens, ids, gates)
     barrier()
     start.record(stream)
     for _ in range(args.steps):
@@ -523,9 +540,12 @@ def run_expert_parallel(args, peaks, world, rank, local_rank):
     gemm_ms = [s.elapsed_time(e) for s, e in layer.gemm_events]
     layer.gemm_events = None
     launches_per_step = layer.launches_last_call
-    # keep the same work running until the 100 ms clock sampler has seen it
-    t_end = time.time() + 0.6
-    while time.time() < t_end:
+    # keep the same work running until the 100 ms clock sampler has seen it; every rank runs
+    # the same number of steps (the exchange is collective), taken from the slowest rank's time
+    ms_all = torch.tensor([total_ms / args.steps], device=dev)
+    if world > 1:
+      dist.all_reduce(ms_all, op=dist.ReduceOp.MAX)
+    for _ in range(int(min(2000, max(10, 700.0 / max(ms_all.item(), 1e-3))))):
       layer(tokens, ids, gates)
     barrier()
   _capi.device_status()
@@ -581,11 +601,13 @@ def run_expert_parallel(args, peaks, world, rank, local_rank):
   g_ms = float(stats[2])
   peak_tf = peaks["bf16_sustained"]                        # a kernel timed inside a long step
   rl = roofline_entry(g_flops, g_bytes, g_ms, peaks, peak_tf) if g_ms > 0 else None
+  full_size = (EP_TOKENS, EP_G) == (8192, 256)
+  ep_traffic = 4.0 * NCU_TRAFFIC_EP_QUARTER if world == 1 and full_size and layer.exchange == "fused" else None
   if rl is not None:
     hbm = rl["bound"] == "hbm"
     roofline = {"bound": rl["bound"], "achieved": rl["gbs"] if hbm else rl["tflops"],
                 "peak": peaks["hbm"] if hbm else peak_tf, "unit": "GB/s" if hbm else UNIT,
-                "frac": rl["frac"], "traffic": None, "kernel": layer.gemm_kernel_name,
+                "frac": rl["frac"], "traffic": ep_traffic, "kernel": layer.gemm_kernel_name,
                 "ms_per_launch": g_ms, "algorithmic_flops_per_launch": g_flops,
                 "algorithmic_bytes_per_launch": g_bytes, "frac_tensor": rl["frac_tensor"],
                 "frac_hbm": rl["frac_hbm"],
