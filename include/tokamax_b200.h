@@ -324,8 +324,8 @@ TKMX_API int tkmx_moe_sort_pairs_inverse(const int32_t* expert_ids, int64_t num_
  *
  * Buffers every rank allocates in memory its peers can address, with the same sizes everywhere:
  *   recv     [capacity_rows, k]  token rows this rank's experts receive, (local expert, source) order
- *   arrive   uint32[G/W + 1]     rows arrived per local expert; the last word is this rank's
- *                                multiplication progress, on which its senders pace themselves
+ *   arrive   uint32[G/W + 2]     rows arrived per local expert; the last two words are this rank's
+ *                                multiplication progress and the cursor its senders draw work from
  *   ret      [T * top_k, n]      this rank's pairs' output rows in expert-sorted order
  *   counts   int32[W, G]         every rank's per-expert pair counts
  *   flags    uint32[W]           barrier flags, zero before the first call

@@ -52,7 +52,7 @@ class VirtualRanks:
     self.w, self.g, self.gl, self.pairs, self.cap = w, g, g // w, t * top_k, w * t * top_k
     mk = lambda shape, dt: [torch.zeros(shape, dtype=dt, device=dev) for _ in range(w)]
     self.recv = mk((self.cap, k), dtype)
-    self.arrive = mk((self.gl + 1,), torch.int32)
+    self.arrive = mk((self.gl + 2,), torch.int32)
     self.ret = mk((self.pairs, n), dtype)
     self.counts = mk((w, g), torch.int32)
     self.flags = mk((w,), torch.int32)

@@ -184,7 +184,7 @@ ep_exchange_plan_kernel(const EpExchangeParams x) {
   if (tid == 0) s_abort = 0;
   // 0. what the peers add to during this step starts at zero; they can only start adding
   //    after they have seen this rank's flag below.
-  for (int i = tid; i <= gl; i += blockDim.x) x.arrive[i] = 0u;    // [gl] is the multiplication progress word
+  for (int i = tid; i <= gl + 1; i += blockDim.x) x.arrive[i] = 0u;   // [gl]: multiplication progress, [gl + 1]: send cursor
   // 1. this rank's counts into row `rank` of every rank's matrix
   for (int idx = tid; idx < W * G; idx += blockDim.x) {
     const int peer = idx / G, e = idx - peer * G;
@@ -267,6 +267,8 @@ struct EpFusedParams {
   const uint64_t* peer_tab;      // device, see EpTab
   const uint32_t* arrive;        // local arrival counters [G/W]
   uint32_t* progress;            // local word (arrive[G/W]): 1 + furthest local expert whose tiles have been started
+  uint32_t* send_cursor;         // local word (arrive[G/W + 1]): next send item to hand out
+  int32_t static_items;          // 1: deal items round-robin to the sender warps instead
   int32_t ahead_rows;            // senders stay at most this many receive-buffer rows ahead of `progress` (0: no pacing)
   int32_t world, rank, top_k;
   int32_t num_experts;           // global G
@@ -285,7 +287,20 @@ __device__ __forceinline__ void ep_send_rows(const EpFusedParams& ep, const int*
   const int P = s_vstart[G];
   const int num_items = (P + kEpItemRows - 1) / kEpItemRows;
   constexpr int kU = 14;  // 16-byte pieces in flight per lane (7 KiB per warp)
-  for (int item = sender; item < num_items; item += num_senders) {
+  // Items are handed out through a counter, not dealt round-robin: an expert can be multiplied
+  // only when ALL its rows have arrived, so one slow warp with a fixed share would hold up
+  // every rank's multiplication; this way items complete in order whatever the warps' speeds.
+  // (Measured on 8 GPUs the two are equal, 2.65 against 2.66 ms per step: `static_items`.)
+  int next_static = sender;
+  while (true) {
+    int item = next_static;
+    if (ep.static_items) {
+      next_static += num_senders;
+    } else {
+      if (lane == 0) item = static_cast<int>(atomicAdd(ep.send_cursor, 1u));
+      item = __shfl_sync(0xffffffffu, item, 0);
+    }
+    if (item >= num_items) break;
     const int i = item * kEpItemRows + lane;
     bool act = lane < kEpItemRows && i < P;
     int v = 0;

@@ -445,6 +445,8 @@ int run_rows(const void* a, const void* b, bool b_cols_contiguous, const int32_t
   p.swap_rows = (rc.pair && rc.block_n == 256 && !gateup && quant_sub == 0) ? env_int("TKMX_SWAP_ROWS", 192, 0, 192) : 0;
   p.out_scales = out_scales;
   p.quant_sub = quant_sub;
+  p.prefetch_blocks = env_int("TKMX_PREFETCH", 0, 0, 64);
+  p.prefetch_cold_only = env_int("TKMX_PREFETCH_COLD_ONLY", 1, 0, 1);
   // Equal swapped tiles instead of full + short ones: off by default.  Measured on B200 it
   // lost (cfg4: 0.40 against 0.24 ms): a swapped tile's transposed epilogue stores 2 bytes per
   // lane and grows with the tile's rows, which outweighs the MMA time saved.
@@ -1303,6 +1305,8 @@ int tkmx_ep_moe_fused(const void* tokens, const int32_t* sorted_pair, const void
   ep.capacity_rows = int32_t(capacity_rows);
   ep.phases = phases;
   ep.progress = const_cast<uint32_t*>(arrive_local) + gl;
+  ep.send_cursor = const_cast<uint32_t*>(arrive_local) + gl + 1;
+  ep.static_items = env_int("TKMX_EP_STATIC_ITEMS", 0, 0, 1);
   // Senders stay at most this much of the receive buffer ahead of the multiplication (rows sent
   // earlier than that have left L2 by the time they are multiplied).  TKMX_EP_AHEAD_MB = 0: no pacing.
   ep.ahead_rows = int32_t(std::min<int64_t>(int64_t(env_int("TKMX_EP_AHEAD_MB", 0, 0, 4096)) * (1 << 20) / (k * 2),

@@ -103,6 +103,7 @@ struct RaggedGemmParams {
   int32_t* sched_counter;      // fp8 kernel: zeroed tile counter for dynamic scheduling, or null (static)
   int32_t mixed_order;         // fp8 kernel visiting order: 0 = by index, 1 = small and large groups merged, 2 = large groups first
   int32_t swap_rows;           // tiles with at most this many rows swap the MMA operands (0: never); see kernels
+  int32_t prefetch_cold_only;  // 1: `prefetch_blocks` applies only to groups that fit one row tile
   int32_t balance_tiles;       // 1: cut multi-tile groups into equal swapped tiles where possible (see TileWalker)
   float* out_scales;           // fused output quantisation: scales [M, cols / quant_sub], else null
   int32_t quant_sub;           // columns per output scale (64, 128 or 256; divides the tile width), 0 = off
@@ -210,11 +211,16 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
 // user of the word).  After that every draw is one atomicAdd, whose result the caller should
 // not look at before it has other work out of the way (the round trip is ~1 us).
 __device__ __forceinline__ void claim_word(unsigned long long* word, uint32_t epoch) {
-  unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(word);
-  while (static_cast<uint32_t>(old >> 32) != epoch) {
-    const unsigned long long seen = atomicCAS(word, old, static_cast<unsigned long long>(epoch) << 32);
-    if (seen == old) break;
-    old = seen;
+  // word[1] (units finished, see finish_drawing) first: every unit leaves here having seen this
+  // launch's epoch in it, so finish_drawing can count with one atomicAdd each.
+#pragma unroll
+  for (int w = 1; w >= 0; --w) {
+    unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(word + w);
+    while (static_cast<uint32_t>(old >> 32) != epoch) {
+      const unsigned long long seen = atomicCAS(word + w, old, static_cast<unsigned long long>(epoch) << 32);
+      if (seen == old) break;
+      old = seen;
+    }
   }
 }
 // Returns the whole (epoch << 32 | tile) word: the caller checks that the epoch is still its
@@ -228,16 +234,11 @@ __device__ __forceinline__ unsigned long long draw_tile(unsigned long long* word
 // unit puts the count back to zero under the same epoch, so that a launch repeated with
 // identical parameters (same word, same epoch) starts from tile 0 again.
 __device__ __forceinline__ void finish_drawing(unsigned long long* word, uint32_t epoch, int num_units) {
-  // word[1] = (epoch << 32 | units finished); a value left by another launch counts as zero.
+  // word[1] = (epoch << 32 | units finished); claim_word put this launch's epoch there.  One
+  // atomicAdd per unit: a compare-and-swap loop here cost tens of microseconds when all units
+  // of a small problem finished together (each success made every other unit retry).
   const unsigned long long fresh = static_cast<unsigned long long>(epoch) << 32;
-  unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(word + 1);
-  unsigned long long mine;
-  while (true) {
-    mine = (static_cast<uint32_t>(old >> 32) == epoch ? old : fresh) + 1ull;
-    const unsigned long long seen = atomicCAS(word + 1, old, mine);
-    if (seen == old) break;
-    old = seen;
-  }
+  const unsigned long long mine = atomicAdd(word + 1, 1ull) + 1ull;
   if (static_cast<uint32_t>(mine) == static_cast<uint32_t>(num_units)) {
     atomicExch(word + 1, fresh);
     __threadfence();
@@ -865,6 +866,20 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             ep_ready_group = t.group;
           }
         }
+        // L2 prefetch of the weight blocks beyond the ring; with `prefetch_cold_only`, only for
+        // groups of a single row tile, whose weights nobody has pulled into L2 before.
+        int prefetch_blocks = p.prefetch_blocks;
+        if (p.prefetch_cold_only && kMode != kContract && t.group >= 0 &&
+            row_start[t.group + 1] - row_start[t.group] > kTileM)
+          prefetch_blocks = 0;
+        if constexpr (kPair && kMode == kRowsBN) {
+          const int ahead = min(prefetch_blocks, t.num_kb);
+          for (int kb = 0; kb < ahead; ++kb) {
+#pragma unroll
+            for (int j = 0; j < kLocalN / 64; ++j)
+              ptx::tma_prefetch_l2_3d(&map_b, col0 + 64 * j, kb * kBlockK, slab);
+          }
+        }
         for (int kb = 0; kb < t.num_kb; ++kb, ++cnt, pos.advance(num_stages)) {
           const uint32_t s = pos.slot;
           const uint32_t ph = pos.phase;
@@ -933,10 +948,10 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                   ptx::tma_load_3d_pair(sb + j * kChunkBytes, &map_b, col0 + 64 * j, kb * kBlockK, slab, full);
                 // Weights that are used by one tile only come from HBM: ask L2 for the blocks
                 // beyond the shared-memory ring, so more bytes are in flight than the ring holds.
-                if (p.prefetch_blocks > 0 && kb + p.prefetch_blocks < t.num_kb) {
+                if (prefetch_blocks > 0 && kb + prefetch_blocks < t.num_kb) {
 #pragma unroll
                   for (int j = 0; j < kLocalN / 64; ++j)
-                    ptx::tma_prefetch_l2_3d(&map_b, col0 + 64 * j, (kb + p.prefetch_blocks) * kBlockK, slab);
+                    ptx::tma_prefetch_l2_3d(&map_b, col0 + 64 * j, (kb + prefetch_blocks) * kBlockK, slab);
                 }
               } else {
                 ptx::tma_load_3d_pair(sb, &map_b, kb * kBlockK, col0, slab, full);

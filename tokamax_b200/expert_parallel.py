@@ -414,7 +414,7 @@ class ExpertParallelMoE:
       raise NotImplementedError(f"the fused exchange serves up to {_capi.EP_MAX_WORLD} ranks")
     pairs = t * top_k
     cap = w * pairs
-    shapes = dict(recv=((cap, k), tokens.dtype), arrive=((gl + 1,), torch.int32), ret=((pairs, n), tokens.dtype),
+    shapes = dict(recv=((cap, k), tokens.dtype), arrive=((gl + 2,), torch.int32), ret=((pairs, n), tokens.dtype),
                   counts=((w, g), torch.int32), flags=((w,), torch.int32))
     bufs, ptrs = {}, {}
     if w > 1:
