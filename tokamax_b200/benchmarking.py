@@ -129,17 +129,45 @@ def _time_cuda(fn: Callable[[], Any], iterations: int, warmup: int) -> tuple[flo
   probe_end.record()
   probe_end.synchronize()
   inner = int(min(32, max(1, 2.0 // max(probe_start.elapsed_time(probe_end), 1e-3))))
+  # Functions shorter than the host needs to issue them (a few tenths of a millisecond through
+  # the op layer) would be timed at the host's pace: record the burst into a CUDA graph and
+  # time its replays.  A function that cannot be captured (it synchronises) is timed eagerly.
+  graph = _capture(fn, inner) if inner > 1 else None
   times = []
   for _ in range(iterations):
     start = torch.cuda.Event(enable_timing=True)
     end = torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(inner):
-      fn()
+    if graph is not None:
+      graph.replay()
+    else:
+      for _ in range(inner):
+        fn()
     end.record()
     end.synchronize()
     times.append(start.elapsed_time(end) / inner)
   return tuple(times)
+
+
+def _capture(fn: Callable[[], Any], count: int):
+  """`count` calls of `fn` as one CUDA graph, or None if `fn` cannot be captured."""
+  stream = torch.cuda.Stream()
+  stream.wait_stream(torch.cuda.current_stream())
+  graph = torch.cuda.CUDAGraph()
+  try:
+    with torch.cuda.stream(stream):
+      fn()
+      stream.synchronize()
+      with torch.cuda.graph(graph, stream=stream):
+        for _ in range(count):
+          fn()
+    torch.cuda.current_stream().wait_stream(stream)
+    graph.replay()          # once untimed: the first replay uploads the graph
+    torch.cuda.synchronize()
+    return graph
+  except Exception:  # pylint: disable=broad-except
+    torch.cuda.synchronize()
+    return None
 
 
 def compile_benchmark(f: Callable, x: Any) -> Callable[..., BenchmarkData]:
