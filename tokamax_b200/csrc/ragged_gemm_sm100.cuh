@@ -499,16 +499,26 @@ enum ElementAct : int {
   kActSigmoid = 6,
 };
 
-__device__ __forceinline__ float element_act(int kind, float x) {
-  switch (kind) {
-    case kActRelu: return fmaxf(x, 0.f);
-    case kActSilu: return x / (1.f + expf(-x));
-    case kActGeluTanh: return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
-    case kActGeluErf: return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
-    case kActTanh: return tanhf(x);
-    case kActSigmoid: return 1.f / (1.f + expf(-x));
+// Applied to 32 accumulator values held in registers.  The switch stands outside the
+// loops: inlined per element, 32 copies of all six bodies made the epilogue code so large
+// that even the path that applies nothing ran from instruction-cache misses (a swapped
+// 128-row tile took 27 us instead of ~5).
+__device__ __forceinline__ void element_act32(int kind, uint32_t (&v)[32]) {
+#define TKMX_ACT_LOOP(expr)                                             \
+  _Pragma("unroll") for (int i = 0; i < 32; ++i) {                      \
+    const float x = __uint_as_float(v[i]);                              \
+    v[i] = __float_as_uint(expr);                                       \
   }
-  return x;
+  switch (kind) {
+    case kActRelu: TKMX_ACT_LOOP(fmaxf(x, 0.f)) break;
+    case kActSilu: TKMX_ACT_LOOP(x / (1.f + expf(-x))) break;
+    case kActGeluTanh: TKMX_ACT_LOOP(0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)))) break;
+    case kActGeluErf: TKMX_ACT_LOOP(0.5f * x * (1.f + erff(x * 0.7071067811865476f))) break;
+    case kActTanh: TKMX_ACT_LOOP(tanhf(x)) break;
+    case kActSigmoid: TKMX_ACT_LOOP(1.f / (1.f + expf(-x))) break;
+    default: break;
+  }
+#undef TKMX_ACT_LOOP
 }
 
 __device__ __forceinline__ float gateup_act(int kind, float g, float u) {
@@ -553,10 +563,7 @@ __device__ __forceinline__ void store_chunk(const RaggedGemmParams& p, uint32_t 
       v[i] = __float_as_uint(__uint_as_float(v[i]) + b);
     }
   }
-  if (p.activation != 0) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(element_act(p.activation, __uint_as_float(v[i])));
-  }
+  if (p.activation != 0) element_act32(p.activation, v);
   if (!row_ok) return;
   if (p.out_is_f32) {
     float* dst = reinterpret_cast<float*>(p.out) + out_row_off + col;
@@ -1196,14 +1203,25 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           }
           const size_t off0 = static_cast<size_t>(t.row0 + rc * 32) * ld_out + n;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (rc * 32 + i < valid && n_ok) {
-              const float val = element_act(p.activation, __uint_as_float(v[i]) * cs + bs);
-              const size_t off = off0 + static_cast<size_t>(i) * ld_out;
-              if (p.out_is_f32) reinterpret_cast<float*>(p.out)[off] = val;
-              else if (p.out_is_f16) reinterpret_cast<__half*>(p.out)[off] = __float2half_rn(val);
-              else reinterpret_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16_rn(val);
-            }
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * cs + bs);
+          if (p.activation != 0) element_act32(p.activation, v);
+          const int nrows = n_ok ? min(32, valid - rc * 32) : 0;
+          const size_t ld = static_cast<size_t>(ld_out);
+          if (p.out_is_f32) {
+            float* dst = reinterpret_cast<float*>(p.out) + off0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < nrows) dst[i * ld] = __uint_as_float(v[i]);
+          } else if (p.out_is_f16) {
+            __half* dst = reinterpret_cast<__half*>(p.out) + off0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < nrows) dst[i * ld] = __float2half_rn(__uint_as_float(v[i]));
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < nrows) dst[i * ld] = __float2bfloat16_rn(__uint_as_float(v[i]));
           }
         }
         ptx::tcgen05_fence_before();
@@ -1281,9 +1299,9 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             for (int i = 0; i < 32; ++i) {
               float x = __uint_as_float(v[i]);
               if (bias_row != nullptr) x += __ldg(bias_row + min(c0 + c * 32 + i, p.cols - 1));
-              if (p.activation != 0) x = element_act(p.activation, x);
               v[i] = __float_as_uint(x);
             }
+            if (p.activation != 0) element_act32(p.activation, v);
           };
 #pragma unroll 1
           for (int c = 0; c < sub / 32; ++c) {
@@ -1387,11 +1405,8 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (use_tma) {
           uint32_t w[32];
           if (p.activation != 0) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              va[i] = __float_as_uint(element_act(p.activation, __uint_as_float(va[i])));
-              vb[i] = __float_as_uint(element_act(p.activation, __uint_as_float(vb[i])));
-            }
+            element_act32(p.activation, va);
+            element_act32(p.activation, vb);
           }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
