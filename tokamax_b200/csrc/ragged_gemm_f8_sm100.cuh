@@ -766,12 +766,14 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float rsi = __shfl_sync(0xffffffffu, my_rs, i);
+              vg[i] = __float_as_uint(__uint_as_float(vg[i]) * rsi * cs_g + bs_g);
+              va[i] = __float_as_uint((acc_value(va[i]) + kLoWeight * acc_value(vb[i])) * rsi * cs_u + bs_u);
+            }
+            gateup_act32(p.gateup, vg, va);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
               const int r = rc * 32 + i;
-              if (r < valid && n_ok) {
-                const float g = __uint_as_float(vg[i]) * rsi * cs_g + bs_g;
-                const float u = (acc_value(va[i]) + kLoWeight * acc_value(vb[i])) * rsi * cs_u + bs_u;
-                store_one(gateup_act(p.gateup, g, u), r, n);
-              }
+              if (r < valid && n_ok) store_one(__uint_as_float(vg[i]), r, n);
             }
           }
         } else {
@@ -824,11 +826,11 @@ ragged_gemm_f8_kernel(const __grid_constant__ CUtensorMap map_a8, const __grid_c
               const float bgv[4] = {bg.x, bg.y, bg.z, bg.w}, buv[4] = {bu.x, bu.y, bu.z, bu.w};
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const float g = __uint_as_float(va[i + j]) * rs * sgv[j] + bgv[j];
-                const float u = __uint_as_float(vb[i + j]) * rs * suv[j] + buv[j];
-                va[i + j] = __float_as_uint(gateup_act(p.gateup, g, u));
+                va[i + j] = __float_as_uint(__uint_as_float(va[i + j]) * rs * sgv[j] + bgv[j]);
+                vb[i + j] = __float_as_uint(__uint_as_float(vb[i + j]) * rs * suv[j] + buv[j]);
               }
             }
+            gateup_act32(p.gateup, va, vb);
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) va[i] = 0u;

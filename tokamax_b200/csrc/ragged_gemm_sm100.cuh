@@ -543,6 +543,30 @@ __device__ __forceinline__ float gateup_act(int kind, float g, float u) {
   return g;
 }
 
+// gateup_act over 32 (gate, up) pairs held in registers; the result replaces the gate values.
+// The switch stands outside the loops for the reason given at element_act32.
+__device__ __forceinline__ void gateup_act32(int kind, uint32_t (&g)[32], const uint32_t (&u)[32]) {
+  switch (kind) {
+    case kGateUpSilu:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(gateup_act(kGateUpSilu, __uint_as_float(g[i]), __uint_as_float(u[i])));
+      break;
+    case kGateUpGelu:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(gateup_act(kGateUpGelu, __uint_as_float(g[i]), __uint_as_float(u[i])));
+      break;
+    case kGateUpSwigluOai:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(gateup_act(kGateUpSwigluOai, __uint_as_float(g[i]), __uint_as_float(u[i])));
+      break;
+    case kGateUpSiluClamp:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(gateup_act(kGateUpSiluClamp, __uint_as_float(g[i]), __uint_as_float(u[i])));
+      break;
+    default: break;
+  }
+}
+
 // Epilogue of one 32-column chunk held by one thread (its row): optional per-column
 // scale, conversion to the output dtype, row- and column-predicated stores.  `ncols` is the
 // width of the output matrix (p.cols unless the epilogue narrows it).
@@ -1255,8 +1279,10 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 gv += __ldg(bias_row + j);
                 uv += __ldg(bias_row + out_cols + j);
               }
-              vg[i] = __float_as_uint(gateup_act(p.gateup, gv, uv));
+              vg[i] = __float_as_uint(gv);
+              vu[i] = __float_as_uint(uv);
             }
+            gateup_act32(p.gateup, vg, vu);
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) vg[i] = 0u;
