@@ -511,7 +511,11 @@ def run_expert_parallel(args, peaks, world, rank, local_rank):
   ids = torch.from_numpy(ids_np).to(dev)
   gates = torch.from_numpy(gates_np).to(dev)
   layer = ExpertParallelMoE(rhs, EP_G, num_chunks=args.ep_chunks if args.ep_chunks > 0 else 4,
-                            exchange=args.ep_exchange)
+                            exchange="fused" if args.ep_exchange in ("fused_once", "fused_pairs") else args.ep_exchange)
+  if args.ep_exchange == "fused_once":
+    layer.once_per_rank = True
+  elif args.ep_exchange == "fused_pairs":
+    layer.once_per_rank = False
   stream = torch.cuda.current_stream()
   sampler_id = gpu_id_for_smi(local_rank) if rank == 0 else None   # rank 0 prints the line
 
@@ -662,8 +666,9 @@ def main():
                   help="weight type of a single-kernel run (cfg3 defaults to fp8)")
   ap.add_argument("--groups", type=int, default=0,
                   help="keep only the first N groups of the workload (smaller profiler captures)")
-  ap.add_argument("--ep-exchange", default=None, choices=[None, "fused", "nccl"],
-                  help="row exchange of the expert-parallel layer (default: the fused kernel)")
+  ap.add_argument("--ep-exchange", default=None, choices=[None, "fused", "fused_once", "fused_pairs", "nccl"],
+                  help="row exchange of the expert-parallel layer (default: the fused kernel; fused_once / "
+                       "fused_pairs force a token to cross to a rank once / once per routed pair)")
   ap.add_argument("--ep-chunks", type=int, default=0,
                   help="expert chunks of the p2p / nccl exchanges whose transfers overlap the neighbouring GEMMs")
   ap.add_argument("--kernel-only", action="store_true",

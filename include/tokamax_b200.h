@@ -366,6 +366,37 @@ TKMX_API int tkmx_ep_moe_fused(const void* tokens, const int32_t* sorted_pair, c
                                int64_t capacity_rows, int dtype, int phases, const tkmx_config* config,
                                void* cuda_stream);
 
+/* The same step with every token crossing the link ONCE PER DESTINATION RANK instead of once per
+ * (token, expert) pair: of a token's pairs on one rank only the one with the lowest expert is
+ * sent; for the others the sender writes a 4-byte reference into the owner's `refs` buffer and
+ * two warps per CTA of the owner copy the row inside the owner's memory once the original is
+ * complete.  With top-8 routing over 8 ranks a token has 4.6 distinct remote owners against 7
+ * remote pairs, so a third of the dispatch bytes stay off the link.  Differences to the calls
+ * above, on every rank alike:
+ *   - one more peer-mapped buffer, refs uint32[capacity_rows], in row 5 of peer_table
+ *     (uint64[6][16]);
+ *   - arrive has tkmx_ep_arrive_words(G, W, 1) = 3 G/W + 3 words, and the plan call is
+ *     tkmx_ep_exchange_plan_words(..., once_per_rank = 1), which resets all of them;
+ *   - expert_ids [num_tokens, top_k] (the ids the pairs were sorted by) and pair_pos (the `pos`
+ *     output of tkmx_moe_sort_pairs_inverse) are read by the senders;
+ *   - phases: bit 2 (4) = copy duplicates; the product form is 7.
+ * G/W <= 254 and capacity_rows <= 2^24, else TKMX_ERR_UNSUPPORTED.  With expert_ids and pair_pos
+ * both NULL the call is tkmx_ep_moe_fused. */
+TKMX_API size_t tkmx_ep_arrive_words(int32_t num_experts, int32_t world, int32_t once_per_rank);
+TKMX_API int tkmx_ep_exchange_plan_words(const int32_t* my_counts, const uint64_t* peer_table,
+                                         int32_t* counts_all_local, uint32_t* flags_local,
+                                         uint32_t* arrive_local, int32_t* plan, int32_t num_experts,
+                                         int32_t world, int32_t rank, uint32_t sequence, int64_t timeout_ns,
+                                         int32_t once_per_rank, void* cuda_stream);
+TKMX_API int tkmx_ep_moe_fused_once_per_rank(const void* tokens, const int32_t* sorted_pair,
+                                             const int32_t* expert_ids, const int32_t* pair_pos,
+                                             const void* recv_local, const void* rhs_local, const int32_t* plan,
+                                             const uint64_t* peer_table, const uint32_t* arrive_local,
+                                             int64_t num_tokens, int32_t top_k, int64_t k, int64_t n,
+                                             int32_t num_experts, int32_t world, int32_t rank,
+                                             int64_t capacity_rows, int dtype, int phases,
+                                             const tkmx_config* config, void* cuda_stream);
+
 /* Flag barrier across the ranks on the stream (one warp): all earlier work of this stream on
  * every rank is complete and visible when the kernel ends. */
 TKMX_API int tkmx_cross_rank_barrier(const uint64_t* peer_table, uint32_t* flags_local, int32_t world,

@@ -47,17 +47,18 @@ def _dense_moe(tok, ids, gates, rhs):
 class VirtualRanks:
   """W ranks' buffers on one device and the peer table that lists them."""
 
-  def __init__(self, capi, w, g, t, top_k, k, n, dtype=torch.bfloat16):
+  def __init__(self, capi, w, g, t, top_k, k, n, dtype=torch.bfloat16, once=False):
     dev = torch.device("cuda", 0)
     self.w, self.g, self.gl, self.pairs, self.cap = w, g, g // w, t * top_k, w * t * top_k
     mk = lambda shape, dt: [torch.zeros(shape, dtype=dt, device=dev) for _ in range(w)]
     self.recv = mk((self.cap, k), dtype)
-    self.arrive = mk((self.gl + 2,), torch.int32)
+    self.arrive = mk((capi.ep_arrive_words(g, w, once),), torch.int32)
     self.ret = mk((self.pairs, n), dtype)
     self.counts = mk((w, g), torch.int32)
     self.flags = mk((w,), torch.int32)
-    table = torch.zeros((5, capi.EP_MAX_WORLD), dtype=torch.int64)
-    for row, bufs in enumerate((self.recv, self.arrive, self.ret, self.counts, self.flags)):
+    self.refs = [torch.full((self.cap,), 0x7fffffff, dtype=torch.int32, device=dev) for _ in range(w)]   # stale garbage
+    table = torch.zeros((capi.EP_TAB_ROWS, capi.EP_MAX_WORLD), dtype=torch.int64)
+    for row, bufs in enumerate((self.recv, self.arrive, self.ret, self.counts, self.flags, self.refs)):
       for r in range(w):
         table[row, r] = bufs[r].data_ptr()
     self.table = table.to(dev)
@@ -110,7 +111,7 @@ def test_exchange_plan_tables_match_restatement(w, g):
       assert np.array_equal(got[name], want[name]), (r, name)
 
 
-def _run_virtual(capi, w, t, k, n, g, top_k, pair, seed, bad_ids=False, dtype=torch.bfloat16):
+def _run_virtual(capi, w, t, k, n, g, top_k, pair, seed, bad_ids=False, dtype=torch.bfloat16, once=False):
   rng = np.random.default_rng(seed)
   rhs = torch.from_numpy(rng.normal(0, k ** -0.5, (g, k, n)).astype(np.float32)).to(dtype)
   gl = g // w
@@ -124,7 +125,7 @@ def _run_virtual(capi, w, t, k, n, g, top_k, pair, seed, bad_ids=False, dtype=to
       ids[rng.random(ids.shape) < 0.03] = -1
     idss.append(torch.from_numpy(ids))
     gatess.append(torch.from_numpy(gates))
-  vr = VirtualRanks(capi, w, g, t, top_k, k, n, dtype)
+  vr = VirtualRanks(capi, w, g, t, top_k, k, n, dtype, once=once)
   dev = vr.table.device
   cfg = capi.Config(collective=1 if pair else 0)
   d_tok = [x.to(dev) for x in toks]
@@ -136,12 +137,14 @@ def _run_virtual(capi, w, t, k, n, g, top_k, pair, seed, bad_ids=False, dtype=to
   for _ in range(2):
     for r in range(w):
       capi.ep_exchange_plan(vr.my_counts[r], vr.table, vr.counts[r], vr.flags[r], vr.arrive[r], vr.plan[r], g, w,
-                            r, 1, 50_000_000)
-  phases = (3,) if w == 1 else (1, 2)
+                            r, 1, 50_000_000, once_per_rank=once)
+  # once per rank: every rank sends and announces, then every rank copies its duplicates and multiplies
+  phases = ((7,) if once else (3,)) if w == 1 else ((1, 6) if once else (1, 2))
   for ph in phases:
     for r in range(w):
       capi.ep_moe_fused(d_tok[r], vr.sorted_pair[r], vr.recv[r], d_rhs[r], vr.plan[r], vr.table, vr.arrive[r],
-                        top_k, g, w, r, n, phases=ph, config=cfg)
+                        top_k, g, w, r, n, phases=ph, config=cfg,
+                        expert_ids=d_ids[r] if once else None, pair_pos=vr.pos[r] if once else None)
   if dtype == torch.bfloat16:
     ys = [capi.moe_combine(vr.ret[r], vr.pos[r], gatess[r].to(dev), t, top_k) for r in range(w)]
   else:   # the combine kernel takes bf16 rows: weight the returned rows with torch instead
@@ -155,10 +158,28 @@ def _run_virtual(capi, w, t, k, n, g, top_k, pair, seed, bad_ids=False, dtype=to
   # group bookkeeping: exact
   all_ids = torch.cat([i.reshape(-1) for i in idss]).numpy()
   hist = np.bincount(all_ids[(all_ids >= 0) & (all_ids < g)], minlength=g)
+  dups = 0
   for r in range(w):
     got = vr.plan[r][:gl].cpu().numpy()
     assert np.array_equal(got, hist[r * gl:(r + 1) * gl]), f"rank {r}: group sizes"
-    assert np.array_equal(vr.arrive[r][:gl].cpu().numpy(), got), f"rank {r}: arrival counters"
+    arrive = vr.arrive[r].cpu().numpy()
+    if once:
+      announced, copied = arrive[gl + 2:2 * gl + 2], arrive[2 * gl + 2:3 * gl + 2]
+      assert np.array_equal(announced, copied), f"rank {r}: every announced duplicate was copied"
+      assert np.array_equal(arrive[:gl] + copied, got), f"rank {r}: rows present + copied"
+      dups += int(copied.sum())
+    else:
+      assert np.array_equal(arrive[:gl], got), f"rank {r}: arrival counters"
+  if once and w > 1 and top_k > 1 and not bad_ids:
+    # what must have stayed off the link: per source token and REMOTE rank, (its pairs there) - 1
+    want_dups = 0
+    for r in range(w):
+      owner = idss[r].numpy() // gl
+      for d in range(w):
+        if d != r:
+          per_tok = (owner == d).sum(1)
+          want_dups += int(np.maximum(per_tok - 1, 0).sum())
+    assert dups == want_dups and dups > 0, (dups, want_dups)
   for r in range(w):
     want = _dense_moe(toks[r], idss[r], gatess[r], rhs)
     helpers.assert_close(ys[r], want.to(dtype), what=f"virtual rank {r} of {w}")
@@ -176,6 +197,17 @@ def test_fused_single_rank_drops_out_of_range_ids():
 @pytest.mark.parametrize("w,pair", [(2, True), (2, False), (4, True), (8, True)])
 def test_fused_virtual_ranks_match_dense_moe(w, pair):
   _run_virtual(_capi(), w, 256, 192, 320, 32, 4, pair, seed=20 + w)
+
+
+@pytest.mark.parametrize("w,pair", [(2, True), (2, False), (4, True), (8, True)])
+def test_fused_once_per_rank_virtual_ranks_match_dense_moe(w, pair):
+  """A token crosses to a rank once; its other rows there are copied by the owner."""
+  _run_virtual(_capi(), w, 256, 192, 320, 32, 4, pair, seed=40 + w, once=True)
+
+
+def test_fused_once_per_rank_with_dropped_pairs_and_f16():
+  _run_virtual(_capi(), 4, 300, 136, 264, 16, 4, True, seed=51, bad_ids=True, once=True)
+  _run_virtual(_capi(), 2, 200, 136, 264, 16, 3, True, seed=52, dtype=torch.float16, once=True)
 
 
 def test_fused_virtual_ranks_f16_and_ragged_k():

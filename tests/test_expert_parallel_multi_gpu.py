@@ -37,7 +37,9 @@ def _worker(rank, world, port, q, chunks, exchange):
     from tokamax_b200.expert_parallel import ExpertParallelMoE
     rhs, per_rank = _inputs(world)
     gl = G // world
-    layer = ExpertParallelMoE(rhs[rank * gl:(rank + 1) * gl].cuda(), G, num_chunks=chunks, exchange=exchange)
+    layer = ExpertParallelMoE(rhs[rank * gl:(rank + 1) * gl].cuda(), G, num_chunks=chunks,
+                              exchange="fused" if exchange == "fused_once" else exchange)
+    layer.once_per_rank = exchange == "fused_once"   # a token crosses to a rank once
     tok, ids, gates = per_rank[rank]
     y, plan = layer(tok.cuda(), ids.cuda(), gates.cuda())
     y = y.clone()
@@ -60,7 +62,7 @@ def _worker(rank, world, port, q, chunks, exchange):
 
 
 @pytest.mark.parametrize("world,chunks,exchange", [(2, 1, "nccl"), (2, 4, "nccl"), (2, 1, "fused"), (4, 1, "fused"),
-                                                   (4, 2, "nccl")])
+                                                   (4, 2, "nccl"), (2, 1, "fused_once"), (4, 1, "fused_once")])
 def test_multi_gpu_expert_parallel_matches_dense_moe(world, chunks, exchange):
   if torch.cuda.device_count() < world:
     pytest.skip(f"needs {world} GPUs")

@@ -62,6 +62,9 @@ EXPORTED_SYMBOLS = (
     "tkmx_ep_plan_bytes",
     "tkmx_ep_exchange_plan",
     "tkmx_ep_moe_fused",
+    "tkmx_ep_arrive_words",
+    "tkmx_ep_exchange_plan_words",
+    "tkmx_ep_moe_fused_once_per_rank",
     "tkmx_cross_rank_barrier",
     "tkmx_ragged_dot_drhs_window",
     "tkmx_ragged_dot_fwd_quant_out",
@@ -143,6 +146,13 @@ def load() -> ctypes.CDLL:
     lib.tkmx_ep_moe_fused.restype = ctypes.c_int
     lib.tkmx_ep_moe_fused.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i32, i64, i64, i32, i32, i32, i64,
                                       ctypes.c_int, ctypes.c_int, cfgp, vp]
+    lib.tkmx_ep_arrive_words.restype = sz
+    lib.tkmx_ep_arrive_words.argtypes = [i32, i32, i32]
+    lib.tkmx_ep_exchange_plan_words.restype = ctypes.c_int
+    lib.tkmx_ep_exchange_plan_words.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, ctypes.c_uint32, i64, i32, vp]
+    lib.tkmx_ep_moe_fused_once_per_rank.restype = ctypes.c_int
+    lib.tkmx_ep_moe_fused_once_per_rank.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i64, i64, i32, i32,
+                                                    i32, i64, ctypes.c_int, ctypes.c_int, cfgp, vp]
     lib.tkmx_cross_rank_barrier.restype = ctypes.c_int
     lib.tkmx_cross_rank_barrier.argtypes = [vp, vp, i32, i32, ctypes.c_uint32, i64, vp]
     lib.tkmx_moe_sort_workspace_bytes.restype = sz
@@ -356,7 +366,13 @@ def moe_sort_workspace_bytes(num_pairs: int, num_experts: int) -> int:
 
 
 EP_MAX_WORLD = 16
-EP_TAB_RECV, EP_TAB_ARRIVE, EP_TAB_RET, EP_TAB_COUNTS, EP_TAB_FLAGS = range(5)
+EP_TAB_RECV, EP_TAB_ARRIVE, EP_TAB_RET, EP_TAB_COUNTS, EP_TAB_FLAGS, EP_TAB_REFS = range(6)
+EP_TAB_ROWS = 6
+
+
+def ep_arrive_words(num_experts: int, world: int, once_per_rank: bool = False) -> int:
+  """uint32 words of a rank's arrival array (see include/tokamax_b200.h)."""
+  return int(load().tkmx_ep_arrive_words(num_experts, world, 1 if once_per_rank else 0))
 
 
 def ep_plan_ints(num_experts: int, world: int) -> int:
@@ -364,9 +380,18 @@ def ep_plan_ints(num_experts: int, world: int) -> int:
 
 
 def ep_exchange_plan(my_counts, peer_table, counts_all, flags, arrive, plan, num_experts: int, world: int,
-                     rank: int, sequence: int, timeout_ns: int) -> None:
+                     rank: int, sequence: int, timeout_ns: int, once_per_rank: bool = False) -> None:
   """Counts all-gather through peer memory + flag barrier + the step's offset tables."""
   dev = _require_cuda(my_counts, peer_table, counts_all, flags, arrive, plan)
+  if arrive.numel() < ep_arrive_words(num_experts, world, once_per_rank):
+    raise ValueError("arrive is shorter than tkmx_ep_arrive_words says")
+  if once_per_rank:
+    with torch.cuda.device(dev):
+      st = load().tkmx_ep_exchange_plan_words(_ptr(my_counts), _ptr(peer_table), _ptr(counts_all), _ptr(flags),
+                                              _ptr(arrive), _ptr(plan), num_experts, world, rank,
+                                              sequence & 0xFFFFFFFF, timeout_ns, 1, _stream(dev))
+    check(st, "tkmx_ep_exchange_plan_words")
+    return
   with torch.cuda.device(dev):
     st = load().tkmx_ep_exchange_plan(_ptr(my_counts), _ptr(peer_table), _ptr(counts_all), _ptr(flags),
                                       _ptr(arrive), _ptr(plan), num_experts, world, rank,
@@ -375,9 +400,23 @@ def ep_exchange_plan(my_counts, peer_table, counts_all, flags, arrive, plan, num
 
 
 def ep_moe_fused(tokens, sorted_pair, recv, rhs_local, plan, peer_table, arrive, top_k: int, num_experts: int,
-                 world: int, rank: int, n: int, phases: int = 3, config: Config | None = None) -> None:
-  """The fused dispatch + grouped GEMM + return kernel (see include/tokamax_b200.h)."""
-  dev = _require_cuda(tokens, sorted_pair, recv, rhs_local, plan, peer_table, arrive)
+                 world: int, rank: int, n: int, phases: int = 3, config: Config | None = None,
+                 expert_ids=None, pair_pos=None) -> None:
+  """The fused dispatch + grouped GEMM + return kernel (see include/tokamax_b200.h).  With
+  `expert_ids` and `pair_pos` a token crosses the link once per destination rank."""
+  dev = _require_cuda(tokens, sorted_pair, recv, rhs_local, plan, peer_table, arrive, expert_ids, pair_pos)
+  if expert_ids is not None or pair_pos is not None:
+    if expert_ids is None or pair_pos is None or expert_ids.dtype != torch.int32 or pair_pos.dtype != torch.int32:
+      raise ValueError("expert_ids and pair_pos must both be int32 tensors")
+    if peer_table.shape[0] < EP_TAB_ROWS or arrive.numel() < ep_arrive_words(num_experts, world, True):
+      raise ValueError("the once-per-rank form needs the six-row peer table and the longer arrival array")
+    with torch.cuda.device(dev):
+      st = load().tkmx_ep_moe_fused_once_per_rank(
+          _ptr(tokens), _ptr(sorted_pair), _ptr(expert_ids), _ptr(pair_pos), _ptr(recv), _ptr(rhs_local),
+          _ptr(plan), _ptr(peer_table), _ptr(arrive), tokens.shape[0], top_k, tokens.shape[1], n, num_experts,
+          world, rank, recv.shape[0], dtype_code(tokens.dtype), phases, _cfg(config), _stream(dev))
+    check(st, "tkmx_ep_moe_fused_once_per_rank")
+    return
   with torch.cuda.device(dev):
     st = load().tkmx_ep_moe_fused(_ptr(tokens), _ptr(sorted_pair), _ptr(recv), _ptr(rhs_local), _ptr(plan),
                                   _ptr(peer_table), _ptr(arrive), tokens.shape[0], top_k, tokens.shape[1], n,

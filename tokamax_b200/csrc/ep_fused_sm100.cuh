@@ -39,7 +39,18 @@ constexpr int kEpMaxWorld = 16;
 constexpr int kEpItemRows = 8;     // rows a send warp moves between two arrival signals
 // Rows of the peer table (device array uint64[kEpTabRows][kEpMaxWorld], entry [t][r] = address
 // of buffer t on rank r as mapped into this process).
-enum EpTab : int { kTabRecv = 0, kTabArrive = 1, kTabRet = 2, kTabCounts = 3, kTabFlags = 4, kEpTabRows = 5 };
+// Row kTabRefs is read only by the form that sends a token once per destination rank.
+enum EpTab : int { kTabRecv = 0, kTabArrive = 1, kTabRet = 2, kTabCounts = 3, kTabFlags = 4, kTabRefs = 5, kEpTabRows = 6 };
+constexpr int kEpCopyWarps = 2;    // sender warps per CTA that copy duplicate rows into place instead
+
+// Words of a rank's arrival array (uint32), G/W = gl local experts:
+//   [0, gl)            rows present per local expert, written by their senders
+//   [gl]               multiplication progress      [gl + 1]  send cursor
+// and, with one row per (token, destination rank) only:
+//   [gl + 2, 2gl + 2)  duplicate rows announced per local expert (their reference word is written)
+//   [2gl + 2, 3gl + 2) duplicate rows copied into place per local expert
+//   [3gl + 2]          copy cursor
+__host__ __device__ inline int ep_arrive_words(int gl, bool once_per_rank) { return once_per_rank ? 3 * gl + 3 : gl + 2; }
 
 constexpr int kDevTimeoutBarrier = 5;    // device status codes (continuing DeviceStatus)
 constexpr int kDevTimeoutArrival = 6;
@@ -144,6 +155,7 @@ struct EpExchangeParams {
   uint32_t seq;
   uint64_t timeout_ns;
   int32_t* status;
+  int32_t arrive_words;       // words of `arrive` to reset (ep_arrive_words)
 };
 
 // Exclusive block-wide prefix sum over 1024 threads; `total` receives the sum.
@@ -184,7 +196,7 @@ ep_exchange_plan_kernel(const EpExchangeParams x) {
   if (tid == 0) s_abort = 0;
   // 0. what the peers add to during this step starts at zero; they can only start adding
   //    after they have seen this rank's flag below.
-  for (int i = tid; i <= gl + 1; i += blockDim.x) x.arrive[i] = 0u;   // [gl]: multiplication progress, [gl + 1]: send cursor
+  for (int i = tid; i < x.arrive_words; i += blockDim.x) x.arrive[i] = 0u;   // layout: ep_arrive_words
   // 1. this rank's counts into row `rank` of every rank's matrix
   for (int idx = tid; idx < W * G; idx += blockDim.x) {
     const int peer = idx / G, e = idx - peer * G;
@@ -275,8 +287,18 @@ struct EpFusedParams {
   int32_t row_vec;               // 16-byte pieces per token row
   int32_t ret_row_bytes;         // bytes per output row
   int32_t capacity_rows;         // rows of every receive buffer
-  int32_t phases;                // bit 0: send this rank's rows; bit 1: multiply and return
+  int32_t phases;                // bit 0: send this rank's rows; bit 1: multiply and return; bit 2: copy duplicates
+  // One row per (token, destination rank): a token routed to several experts of one rank crosses
+  // the link once, for its lowest expert there; for the others the sender writes a reference
+  // word and the destination copies the row inside its own memory.  All zero when off.
+  int32_t once_per_rank;
+  const int32_t* expert_ids;     // [T, top_k] global expert of every pair
+  const int32_t* pair_pos;       // [T * top_k] expert-sorted position of every pair
 };
+
+// Reference word of a receive-buffer row: 0 = the row itself arrives; otherwise
+// (local expert of the original + 1) << 24 | receive-buffer row of the original.
+constexpr int kEpRefRowBits = 24;
 
 // Sending side, one warp: rows in send order (local expert major, then owner), kEpItemRows at a
 // time, so that every owner receives its first experts first.
@@ -291,10 +313,11 @@ __device__ __forceinline__ void ep_send_rows(const EpFusedParams& ep, const int*
   // only when ALL its rows have arrived, so one slow warp with a fixed share would hold up
   // every rank's multiplication; this way items complete in order whatever the warps' speeds.
   // (Measured on 8 GPUs the two are equal, 2.65 against 2.66 ms per step: `static_items`.)
+  const int gl = G / W;
   int next_static = sender;
   while (true) {
     int item = next_static;
-    if (ep.static_items) {
+    if (ep.static_items && !ep.once_per_rank) {
       next_static += num_senders;
     } else {
       if (lane == 0) item = static_cast<int>(atomicAdd(ep.send_cursor, 1u));
@@ -305,6 +328,7 @@ __device__ __forceinline__ void ep_send_rows(const EpFusedParams& ep, const int*
     bool act = lane < kEpItemRows && i < P;
     int v = 0;
     uint64_t src = 0, dst = 0;
+    bool dup = false;       // this row is a token's second or later row on its destination rank
     if (act) {
       int lo = 0, hi = G;            // largest v with vstart[v] <= i
       while (hi - lo > 1) {
@@ -323,6 +347,40 @@ __device__ __forceinline__ void ep_send_rows(const EpFusedParams& ep, const int*
         const size_t row_bytes = static_cast<size_t>(ep.row_vec) * 16;
         src = reinterpret_cast<uint64_t>(ep.tokens) + static_cast<size_t>(pair / ep.top_k) * row_bytes;
         dst = __ldg(ep.peer_tab + kTabRecv * kEpMaxWorld + (v % W)) + static_cast<size_t>(drow) * row_bytes;
+        if (ep.once_per_rank) {
+          // The original of a token on a rank is its pair with the lowest (expert, pair index)
+          // there: the first of them in send order, so it is complete before its copies are due.
+          const int owner = v % W;
+          uint32_t ref = 0u;
+          if (owner != ep.rank) {
+            const int tok = pair / ep.top_k;
+            const int e = owner * gl + v / W;
+            int best_e = e, best_pair = pair;
+            for (int j = 0; j < ep.top_k; ++j) {
+              const int pj = tok * ep.top_k + j;
+              const int ej = __ldg(ep.expert_ids + pj);
+              if (ej >= owner * gl && ej < (owner + 1) * gl && (ej < best_e || (ej == best_e && pj < best_pair))) {
+                best_e = ej;
+                best_pair = pj;
+              }
+            }
+            if (best_pair != pair) {
+              const int le1 = best_e - owner * gl;
+              const int v1 = le1 * W + owner;
+              const int r1 = __ldg(ep.plan + L.dst_row + v1) + __ldg(ep.pair_pos + best_pair) - __ldg(ep.plan + L.src_off + v1);
+              if (r1 < 0 || r1 >= ep.capacity_rows || r1 >= (1 << kEpRefRowBits)) {
+                atomicCAS(status, 0, kDevEpOverflow);
+              } else {
+                dup = true;
+                src = 0;    // nothing to move
+                ref = (static_cast<uint32_t>(le1 + 1) << kEpRefRowBits) | static_cast<uint32_t>(r1);
+              }
+            }
+          }
+          // Every row's reference word is written (0: the row itself arrives) before the counter
+          // update that tells the owner about the row.
+          *(reinterpret_cast<uint32_t*>(__ldg(ep.peer_tab + kTabRefs * kEpMaxWorld + owner)) + drow) = ref;
+        }
       }
     }
     const int nrows = min(kEpItemRows, P - item * kEpItemRows);
@@ -362,13 +420,122 @@ __device__ __forceinline__ void ep_send_rows(const EpFusedParams& ep, const int*
     // Every lane's stores are ordered before the counter update the owner acquires.
     __threadfence_system();
     __syncwarp();
-    const unsigned m = __ballot_sync(0xffffffffu, act);
-    if (act) {
+    const unsigned m = __ballot_sync(0xffffffffu, act && !dup);
+    if (act && !dup) {
       const unsigned same = __match_any_sync(m, v);
       if (lane == __ffs(same) - 1) {
         uint32_t* ctr = reinterpret_cast<uint32_t*>(__ldg(ep.peer_tab + kTabArrive * kEpMaxWorld + (v % W))) + v / W;
         ptx::red_release_sys_add_u32(ctr, __popc(same));
       }
+    }
+    const unsigned md = __ballot_sync(0xffffffffu, act && dup);
+    if (act && dup) {
+      const unsigned same = __match_any_sync(md, v);
+      if (lane == __ffs(same) - 1) {   // "announced" counters follow the arrival ones, see ep_arrive_words
+        uint32_t* ctr = reinterpret_cast<uint32_t*>(__ldg(ep.peer_tab + kTabArrive * kEpMaxWorld + (v % W))) + gl + 2 + v / W;
+        ptx::red_release_sys_add_u32(ctr, __popc(same));
+      }
+    }
+  }
+}
+
+// Bounded wait of one thread until a[0] + b[0] >= expected (b may be null).
+__device__ __forceinline__ bool ep_wait_sum(const uint32_t* a, const uint32_t* b, uint32_t expected,
+                                            volatile int* abort_flag, int32_t* status, uint64_t budget_ns) {
+  auto seen = [&]() { return ptx::ld_acquire_sys_u32(a) + (b != nullptr ? ptx::ld_acquire_sys_u32(b) : 0u); };
+  if (seen() >= expected) return true;
+  const uint64_t t0 = ptx::gtimer_ns();
+  uint32_t spins = 0;
+  while (seen() < expected) {
+    if ((++spins & 0x3Fu) == 0) {
+      if (*abort_flag) return false;
+      if (ptx::gtimer_ns() - t0 > budget_ns) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, kDevTimeoutArrival);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Receiving side of the once-per-rank form, one warp: rows of this rank's receive buffer,
+// kEpItemRows at a time in expert order.  Once every row of an expert is either present or
+// announced (its reference word is written), the duplicates among them are copied from their
+// originals, which lie in an earlier expert of the same buffer, and counted as copied.
+// `row_start` [G/W + 1]: first receive-buffer row of every local expert (shared memory).
+__device__ __forceinline__ void ep_copy_rows(const EpFusedParams& ep, const int* row_start, int lane,
+                                             volatile int* abort_flag, int32_t* status, uint64_t budget_ns) {
+  const int gl = ep.num_experts / ep.world;
+  const int R = row_start[gl];
+  const int num_items = (R + kEpItemRows - 1) / kEpItemRows;
+  const uint32_t* present = ep.arrive;
+  const uint32_t* announced = ep.arrive + gl + 2;
+  uint32_t* copied = const_cast<uint32_t*>(ep.arrive) + 2 * gl + 2;
+  uint32_t* cursor = const_cast<uint32_t*>(ep.arrive) + 3 * gl + 2;
+  const uint32_t* refs = reinterpret_cast<const uint32_t*>(__ldg(ep.peer_tab + kTabRefs * kEpMaxWorld + ep.rank));
+  const uint64_t recv = __ldg(ep.peer_tab + kTabRecv * kEpMaxWorld + ep.rank);
+  const size_t row_bytes = static_cast<size_t>(ep.row_vec) * 16;
+  constexpr int kU = 14;
+  while (true) {
+    int item = 0;
+    if (lane == 0) item = static_cast<int>(atomicAdd(cursor, 1u));
+    item = __shfl_sync(0xffffffffu, item, 0);
+    if (item >= num_items) break;
+    const int row = item * kEpItemRows + lane;
+    const bool act = lane < kEpItemRows && row < R;
+    int le = 0;
+    bool ok = true;
+    if (act) {
+      int lo = 0, hi = gl;            // largest le with row_start[le] <= row (empty experts share a start: the last one holds the row)
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (row_start[mid] <= row) lo = mid;
+        else hi = mid;
+      }
+      le = lo;
+      ok = ep_wait_sum(present + le, announced + le, static_cast<uint32_t>(row_start[le + 1] - row_start[le]),
+                       abort_flag, status, budget_ns);
+    }
+    uint64_t src = 0, dst = 0;
+    bool dup = false;
+    if (act && ok) {
+      const uint32_t ref = static_cast<uint32_t>(ptx::ld_relaxed_sys_s32(reinterpret_cast<const int32_t*>(refs + row)));
+      if (ref != 0u) {
+        const int le1 = static_cast<int>(ref >> kEpRefRowBits) - 1;
+        const int r1 = static_cast<int>(ref & ((1u << kEpRefRowBits) - 1u));
+        if (le1 < 0 || le1 >= le || r1 < row_start[le1] || r1 >= row_start[le1 + 1]) {
+          atomicCAS(status, 0, kDevEpOverflow);
+        } else if (ep_wait_sum(present + le1, announced + le1, static_cast<uint32_t>(row_start[le1 + 1] - row_start[le1]),
+                               abort_flag, status, budget_ns)) {
+          dup = true;
+          src = recv + static_cast<size_t>(r1) * row_bytes;
+          dst = recv + static_cast<size_t>(row) * row_bytes;
+        }
+      }
+    }
+    if (__any_sync(0xffffffffu, act && !ok)) break;   // a wait ran out: the status word says so
+    const int nrows = min(kEpItemRows, R - item * kEpItemRows);
+    for (int j = 0; j < nrows; ++j) {
+      const uint4* s4 = reinterpret_cast<const uint4*>(shfl64(src, j));
+      uint4* d4 = reinterpret_cast<uint4*>(shfl64(dst, j));
+      if (s4 == nullptr) continue;   // warp-uniform
+      for (int base = lane; base < ep.row_vec; base += 32 * kU) {
+        uint4 r[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u)
+          if (base + 32 * u < ep.row_vec) r[u] = __ldcg(s4 + base + 32 * u);   // written by a peer during this kernel: not the read-only path
+#pragma unroll
+        for (int u = 0; u < kU; ++u)
+          if (base + 32 * u < ep.row_vec) d4[base + 32 * u] = r[u];
+      }
+    }
+    __threadfence();
+    __syncwarp();
+    const unsigned md = __ballot_sync(0xffffffffu, dup);
+    if (dup) {
+      const unsigned same = __match_any_sync(md, le);
+      if (lane == __ffs(same) - 1) ptx::red_release_sys_add_u32(copied + le, __popc(same));
     }
   }
 }
@@ -376,21 +543,10 @@ __device__ __forceinline__ void ep_send_rows(const EpFusedParams& ep, const int*
 // Receiving side: wait until all `expected` rows of local expert `le` have arrived.  One thread.
 __device__ __forceinline__ bool ep_wait_expert(const EpFusedParams& ep, int le, uint32_t expected,
                                                volatile int* abort_flag, int32_t* status, uint64_t budget_ns) {
+  // Rows present plus, in the once-per-rank form, duplicates copied into place.
   const uint32_t* ctr = ep.arrive + le;
-  if (ptx::ld_acquire_sys_u32(ctr) < expected) {
-    const uint64_t t0 = ptx::gtimer_ns();
-    uint32_t spins = 0;
-    while (ptx::ld_acquire_sys_u32(ctr) < expected) {
-      if ((++spins & 0x3Fu) == 0) {
-        if (*abort_flag) return false;
-        if (ptx::gtimer_ns() - t0 > budget_ns) {
-          *abort_flag = 1;
-          atomicCAS(status, 0, kDevTimeoutArrival);
-          return false;
-        }
-      }
-    }
-  }
+  const uint32_t* copied = ep.once_per_rank ? ep.arrive + 2 * (ep.num_experts / ep.world) + 2 + le : nullptr;
+  if (!ep_wait_sum(ctr, copied, expected, abort_flag, status, budget_ns)) return false;
   ptx::fence_proxy_async_all();   // the rows were written by generic-proxy stores; TMA reads them next
   return true;
 }

@@ -1184,6 +1184,19 @@ int tkmx_cross_rank_barrier(const uint64_t* peer_table, uint32_t* flags_local, i
 int tkmx_ep_exchange_plan(const int32_t* my_counts, const uint64_t* peer_table, int32_t* counts_all_local,
                           uint32_t* flags_local, uint32_t* arrive_local, int32_t* plan, int32_t num_experts,
                           int32_t world, int32_t rank, uint32_t sequence, int64_t timeout_ns, void* cuda_stream) {
+  return tkmx_ep_exchange_plan_words(my_counts, peer_table, counts_all_local, flags_local, arrive_local, plan,
+                                     num_experts, world, rank, sequence, timeout_ns, 0, cuda_stream);
+}
+
+size_t tkmx_ep_arrive_words(int32_t num_experts, int32_t world, int32_t once_per_rank) {
+  if (ep_check_world(num_experts, world, 0) != TKMX_OK) return 0;
+  return size_t(tkmx::ep_arrive_words(num_experts / world, once_per_rank != 0));
+}
+
+int tkmx_ep_exchange_plan_words(const int32_t* my_counts, const uint64_t* peer_table, int32_t* counts_all_local,
+                                uint32_t* flags_local, uint32_t* arrive_local, int32_t* plan, int32_t num_experts,
+                                int32_t world, int32_t rank, uint32_t sequence, int64_t timeout_ns,
+                                int32_t once_per_rank, void* cuda_stream) {
   int st = ep_check_world(num_experts, world, rank);
   if (st != TKMX_OK) return st;
   if (my_counts == nullptr || peer_table == nullptr || counts_all_local == nullptr || flags_local == nullptr ||
@@ -1205,6 +1218,7 @@ int tkmx_ep_exchange_plan(const int32_t* my_counts, const uint64_t* peer_table, 
   x.seq = sequence;
   x.timeout_ns = uint64_t(timeout_ns);
   x.status = dev->status_ptr;
+  x.arrive_words = tkmx::ep_arrive_words(num_experts / world, once_per_rank != 0);
   tkmx::ep_exchange_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(cuda_stream)>>>(x);
   TKMX_CUDA_OK(cudaGetLastError());
   return TKMX_OK;
@@ -1215,10 +1229,28 @@ int tkmx_ep_moe_fused(const void* tokens, const int32_t* sorted_pair, const void
                       const uint32_t* arrive_local, int64_t num_tokens, int32_t top_k, int64_t k, int64_t n,
                       int32_t num_experts, int32_t world, int32_t rank, int64_t capacity_rows, int dtype,
                       int phases, const tkmx_config* config, void* cuda_stream) {
+  return tkmx_ep_moe_fused_once_per_rank(tokens, sorted_pair, nullptr, nullptr, recv_local, rhs_local, plan,
+                                         peer_table, arrive_local, num_tokens, top_k, k, n, num_experts, world,
+                                         rank, capacity_rows, dtype, phases, config, cuda_stream);
+}
+
+int tkmx_ep_moe_fused_once_per_rank(const void* tokens, const int32_t* sorted_pair, const int32_t* expert_ids,
+                                    const int32_t* pair_pos, const void* recv_local, const void* rhs_local,
+                                    const int32_t* plan, const uint64_t* peer_table, const uint32_t* arrive_local,
+                                    int64_t num_tokens, int32_t top_k, int64_t k, int64_t n, int32_t num_experts,
+                                    int32_t world, int32_t rank, int64_t capacity_rows, int dtype, int phases,
+                                    const tkmx_config* config, void* cuda_stream) {
   int st = ep_check_world(num_experts, world, rank);
   if (st != TKMX_OK) return st;
-  if (num_tokens < 0 || top_k <= 0 || k <= 0 || n <= 0 || capacity_rows <= 0 || phases < 1 || phases > 3)
+  // Both arrays given: a token crosses the link once per destination rank.
+  const bool once = expert_ids != nullptr || pair_pos != nullptr;
+  if (once && (expert_ids == nullptr || pair_pos == nullptr)) return TKMX_ERR_INVALID_ARGUMENT;
+  if (num_tokens < 0 || top_k <= 0 || k <= 0 || n <= 0 || capacity_rows <= 0 || phases < 1 ||
+      phases > (once ? 7 : 3))
     return TKMX_ERR_INVALID_ARGUMENT;
+  // reference words hold (local expert + 1) in 8 bits and a receive-buffer row in 24
+  if (once && (num_experts / world > 254 || capacity_rows > (int64_t(1) << tkmx::kEpRefRowBits)))
+    return TKMX_ERR_UNSUPPORTED;
   if (dtype != TKMX_BF16 && dtype != TKMX_F16) return TKMX_ERR_UNSUPPORTED;
   if (k % 8 != 0 || n % 8 != 0) return TKMX_ERR_ALIGNMENT;   // rows move and return in 16-byte pieces
   if (!fits_i32(num_tokens * top_k) || !fits_i32(k) || !fits_i32(n) || !fits_i32(capacity_rows) ||
@@ -1307,6 +1339,9 @@ int tkmx_ep_moe_fused(const void* tokens, const int32_t* sorted_pair, const void
   ep.progress = const_cast<uint32_t*>(arrive_local) + gl;
   ep.send_cursor = const_cast<uint32_t*>(arrive_local) + gl + 1;
   ep.static_items = env_int("TKMX_EP_STATIC_ITEMS", 0, 0, 1);
+  ep.once_per_rank = once ? 1 : 0;
+  ep.expert_ids = expert_ids;
+  ep.pair_pos = pair_pos;
   // Senders stay at most this much of the receive buffer ahead of the multiplication (rows sent
   // earlier than that have left L2 by the time they are multiplied).  TKMX_EP_AHEAD_MB = 0: no pacing.
   ep.ahead_rows = int32_t(std::min<int64_t>(int64_t(env_int("TKMX_EP_AHEAD_MB", 0, 0, 4096)) * (1 << 20) / (k * 2),

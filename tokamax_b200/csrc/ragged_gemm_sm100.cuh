@@ -1080,7 +1080,12 @@ ragged_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       // ===== expert-parallel senders: six warps per CTA (2, 3, 8-11), all CTAs of the grid.
       // Consecutive items go to different CTAs, so every SM's links carry every expert. =====
       const int local = warp < 8 ? warp - 2 : warp - 6;
-      if (ep.phases & 1)
+      // Once-per-rank form: kEpCopyWarps of the six put duplicate rows into place in this rank's
+      // own receive buffer (all six in a launch that does not send).
+      const bool copier = ep.once_per_rank && (ep.phases & 4) && (!(ep.phases & 1) || local < kEpCopyWarps);
+      if (copier)
+        ep_copy_rows(ep, row_start, lane, abort_flag, p.status, kWaitBudgetNs);
+      else if (ep.phases & 1)
         ep_send_rows(ep, ep_vstart, (ep.phases & 2) ? ep_need : nullptr,
                      local * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x),
                      kEpSendWarps * static_cast<int>(gridDim.x), lane, p.status);

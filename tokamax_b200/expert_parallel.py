@@ -149,6 +149,9 @@ class ExpertParallelMoE:
     self._fused = None
     self._seq = 0
     self.gemm_config = None          # a `_capi.Config` for the fused kernel's GEMM, or None for a size-based choice
+    # Fused exchange: send a token once per destination RANK and let the owner copy the rows of
+    # its other experts there (set before the first call; needs more than one rank).
+    self.once_per_rank = False
     self.timeout_ns = 2_000_000_000  # budget of every cross-rank flag wait
     self.gemm_events = None          # set to a list to collect (start, end) CUDA events around the grouped GEMM
     self.launches_last_call = 0      # kernels of this library launched by the last call
@@ -249,6 +252,8 @@ class ExpertParallelMoE:
   @property
   def exchange_name(self) -> str:
     if self.exchange == "fused":
+      if self.once_per_rank and self.world > 1:
+        return "fused (peer stores inside the GEMM kernel; a token crosses to a rank once)"
       return "fused (peer stores inside the GEMM kernel)"
     return "nccl all-to-all" if self.world > 1 else "local (gather, GEMM, combine)"
 
@@ -405,7 +410,8 @@ class ExpertParallelMoE:
     from tokamax_b200 import _capi
     t, k = tokens.shape
     n = self.rhs_local.shape[2]
-    key = (t, top_k, k, n, tokens.dtype)
+    once = bool(self.once_per_rank) and self.world > 1
+    key = (t, top_k, k, n, tokens.dtype, once)
     if self._fused is not None and self._fused["key"] == key:
       return self._fused
     dev = tokens.device
@@ -414,8 +420,10 @@ class ExpertParallelMoE:
       raise NotImplementedError(f"the fused exchange serves up to {_capi.EP_MAX_WORLD} ranks")
     pairs = t * top_k
     cap = w * pairs
-    shapes = dict(recv=((cap, k), tokens.dtype), arrive=((gl + 2,), torch.int32), ret=((pairs, n), tokens.dtype),
-                  counts=((w, g), torch.int32), flags=((w,), torch.int32))
+    shapes = dict(recv=((cap, k), tokens.dtype), arrive=((_capi.ep_arrive_words(g, w, once),), torch.int32),
+                  ret=((pairs, n), tokens.dtype), counts=((w, g), torch.int32), flags=((w,), torch.int32))
+    if once:
+      shapes["refs"] = ((cap,), torch.int32)
     bufs, ptrs = {}, {}
     if w > 1:
       import torch.distributed._symmetric_memory as symm_mem
@@ -432,14 +440,16 @@ class ExpertParallelMoE:
         bufs[name] = torch.zeros(shape, dtype=dtype, device=dev) if name != "recv" else torch.empty(
             shape, dtype=dtype, device=dev)
         ptrs[name] = [bufs[name].data_ptr()]
-    table = torch.zeros((5, _capi.EP_MAX_WORLD), dtype=torch.int64)
+    table = torch.zeros((_capi.EP_TAB_ROWS, _capi.EP_MAX_WORLD), dtype=torch.int64)
     for row, name in ((_capi.EP_TAB_RECV, "recv"), (_capi.EP_TAB_ARRIVE, "arrive"), (_capi.EP_TAB_RET, "ret"),
-                      (_capi.EP_TAB_COUNTS, "counts"), (_capi.EP_TAB_FLAGS, "flags")):
+                      (_capi.EP_TAB_COUNTS, "counts"), (_capi.EP_TAB_FLAGS, "flags"), (_capi.EP_TAB_REFS, "refs")):
+      if name not in bufs:
+        continue
       for r in range(w):
         # addresses above 2^63 would not fit int64: CUDA virtual addresses are far below
         table[row, r] = ptrs[name][r]
     self._fused = dict(
-        key=key, cap=cap, bufs=bufs, table=table.to(dev),
+        key=key, cap=cap, bufs=bufs, table=table.to(dev), once=once,
         plan=torch.zeros(_capi.ep_plan_ints(g, w), dtype=torch.int32, device=dev),
         pos=torch.empty(pairs, dtype=torch.int32, device=dev),
         sorted_pair=torch.zeros(pairs, dtype=torch.int32, device=dev),
@@ -478,8 +488,10 @@ class ExpertParallelMoE:
     tokens = tokens.contiguous()
     _capi.moe_sort_pairs_inverse(ids.contiguous(), g, st["pos"], st["sorted_pair"], st["my_counts"], st["sort_ws"])
     self._seq += 1
+    once = st["once"]
+    ids = ids.contiguous()
     _capi.ep_exchange_plan(st["my_counts"], st["table"], b["counts"], b["flags"], b["arrive"], st["plan"], g, w,
-                           self.rank, self._seq, self.timeout_ns)
+                           self.rank, self._seq, self.timeout_ns, once_per_rank=once)
     cfg = self._fused_config(t * top_k)
     n = self.rhs_local.shape[2]
     launches = 3 + 1
@@ -491,8 +503,11 @@ class ExpertParallelMoE:
         self._seq += 1
         _capi.cross_rank_barrier(st["table"], b["flags"], w, self.rank, self._seq, self.timeout_ns)
         launches += 1
+      if once:   # the product form also copies duplicates (bit 2); a multiply-only launch copies first
+        ph = 7 if ph == 3 else (6 if ph == 2 else ph)
       _capi.ep_moe_fused(tokens, st["sorted_pair"], b["recv"], self.rhs_local, st["plan"], st["table"],
-                         b["arrive"], top_k, g, w, self.rank, n, phases=ph, config=cfg)
+                         b["arrive"], top_k, g, w, self.rank, n, phases=ph, config=cfg,
+                         expert_ids=ids if once else None, pair_pos=st["pos"] if once else None)
       launches += 1
     if ev:
       ev[1].record()
