@@ -125,3 +125,51 @@ def ep_plan_ref(counts_all: np.ndarray, rank: int) -> dict:
   i32 = lambda a: np.asarray(a, np.int32)
   return dict(group_sizes=i32(per_expert[mine]), vstart=i32(vstart), src_off=i32(send_off_all[rank][v_to_e]),
               dst_row=i32((expert_start + within[rank])[v_to_e]), seg_start=i32(seg_start), ret_off=i32(ret_off))
+
+
+def ep_reference_words_ref(ids_all, num_experts: int) -> list:
+  """Reference words of the once-per-rank dispatch (include/tokamax_b200.h,
+  tkmx_ep_moe_fused_once_per_rank) for every rank's receive buffer.
+
+  `ids_all`: per source rank an int array [T, top_k] of global expert ids (ids outside
+  [0, num_experts) are dropped pairs).  Of a token's pairs on one REMOTE rank only the one with the
+  lowest (expert, pair index) is shipped; the word of every other such row is
+  (local expert of that original + 1) << 24 | the original's receive-buffer row, and 0 for rows
+  that arrive themselves (originals, and every row a rank sends to itself).
+  Returns per rank an int64 array over its used receive-buffer rows."""
+  w = len(ids_all)
+  g = num_experts
+  gl = g // w
+  counts = np.zeros((w, g), np.int64)
+  sorted_pos = []
+  for s, ids in enumerate(ids_all):
+    pos, cnt = sort_pairs_ref(np.asarray(ids), g)
+    sorted_pos.append(np.asarray(pos).reshape(-1))
+    counts[s] = cnt
+  per_expert = counts.sum(0)
+  pe = per_expert.reshape(w, gl)
+  expert_start = (np.cumsum(pe, 1) - pe).reshape(-1)
+  within = np.cumsum(counts, 0) - counts
+  send_off = np.cumsum(counts, 1) - counts
+  out = [np.zeros(int(pe[d].sum()), np.int64) for d in range(w)]
+
+  def recv_row(s, pair, e):
+    return int(expert_start[e] + within[s, e] + sorted_pos[s][pair] - send_off[s, e])
+
+  for s, ids in enumerate(ids_all):
+    ids = np.asarray(ids)
+    t, top_k = ids.shape
+    for tok in range(t):
+      for j in range(top_k):
+        e = int(ids[tok, j])
+        if e < 0 or e >= g:
+          continue
+        d = e // gl
+        if d == s:
+          continue
+        pair = tok * top_k + j
+        best = min((int(ids[tok, jj]), tok * top_k + jj) for jj in range(top_k)
+                   if 0 <= int(ids[tok, jj]) < g and int(ids[tok, jj]) // gl == d)
+        if best[1] != pair:
+          out[d][recv_row(s, pair, e)] = ((best[0] - d * gl + 1) << 24) | recv_row(s, best[1], best[0])
+  return out

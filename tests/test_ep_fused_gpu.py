@@ -170,6 +170,12 @@ def _run_virtual(capi, w, t, k, n, g, top_k, pair, seed, bad_ids=False, dtype=to
       dups += int(copied.sum())
     else:
       assert np.array_equal(arrive[:gl], got), f"rank {r}: arrival counters"
+  if once:
+    # every reference word, exactly (stale words were pre-set to garbage)
+    want_refs = moe_ref.ep_reference_words_ref([i.numpy() for i in idss], g)
+    for r in range(w):
+      got_refs = vr.refs[r][:len(want_refs[r])].cpu().numpy().astype(np.int64)
+      assert np.array_equal(got_refs, want_refs[r]), f"rank {r}: reference words"
   if once and w > 1 and top_k > 1 and not bad_ids:
     # what must have stayed off the link: per source token and REMOTE rank, (its pairs there) - 1
     want_dups = 0

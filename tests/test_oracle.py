@@ -222,3 +222,22 @@ def test_permutation_op_oracles_known_answers():
   got = moe_ref.ragged_gather_reduce_ref(x, idx, np.array([1.0, 2.0, 0.5, 1.0], np.float32),
                                          np.array([True, True, False, True]), 2)
   assert got.tolist() == [[6, 9, 12], [9, 10, 11]]
+
+
+def test_reference_words_of_the_once_per_rank_dispatch_known_answer():
+  """Two ranks, four experts (two each), hand-checked.  Rank 0's only token goes to experts
+  2, 3 (both on rank 1) and 0 (its own): expert 2's row is shipped, expert 3's row becomes a
+  reference to it, the local row arrives itself.  Rank 1's token goes to experts 1, 0 (both on
+  rank 0, pair order reversed) and 3."""
+  from oracle import moe_ref
+  ids = [np.array([[2, 3, 0]], np.int32), np.array([[1, 0, 3]], np.int32)]
+  refs = moe_ref.ep_reference_words_ref(ids, 4)
+  # rank 0 receives: expert 0 <- rank 0 (row 0), expert 0 <- rank 1 (row 1), expert 1 <- rank 1 (row 2);
+  # of rank 1's two rows here, expert 0 (row 1) is the original, expert 1 refers to it.
+  assert refs[0].tolist() == [0, 0, (1 << 24) | 1]
+  # rank 1 receives: expert 2 <- rank 0 (row 0), expert 3 <- rank 0 (row 1), expert 3 <- rank 1 (row 2)
+  assert refs[1].tolist() == [0, (1 << 24) | 0, 0]
+  # dropped pairs never become originals or references
+  ids2 = [np.array([[2, 9, 3]], np.int32), np.array([[-1, 0, 1]], np.int32)]
+  refs2 = moe_ref.ep_reference_words_ref(ids2, 4)
+  assert refs2[1].tolist() == [0, (1 << 24) | 0] and refs2[0].tolist() == [0, (1 << 24) | 0]
