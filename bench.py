@@ -24,9 +24,10 @@ Qwen3-shaped forward / dlhs / drhs, dsv3 forward / dlhs / drhs and their aggrega
 with its time, TFLOP/s, GB/s and the fraction of max(t_flops, t_bytes) at the measured peaks.
 
 `value` is timed with inputs resident in HBM (CUDA events on the launching stream, max over
-ranks).  `e2e` is the same step through the public API with pinned HOST buffers: tokens,
-routing and gates are copied host->device and the result device->host inside the timed
-region.  `cpu_baseline` (rank 0, N = 1) times the CPU restatement of the reference path on
+ranks).  `e2e` is the same step through the public API with pinned HOST buffers
+(`HostPipeline.submit`): every step's tokens, routing and gates are copied host->device and
+its result device->host inside the timed region, the copies of one step running beside the
+computation of its neighbours; the region ends when the last result is in host memory.  `cpu_baseline` (rank 0, N = 1) times the CPU restatement of the reference path on
 the host cores.  --impl reference times that CPU restatement alone (the reference is pure
 Python over jax/jaxlib, which is not installable here: no oracle/_ref exists).
 
@@ -561,26 +562,27 @@ def run_expert_parallel(args, peaks, world, rank, local_rank):
 
   # end to end: host tokens / routing in, combined activations out
   h_tok, h_ids, h_gates = tokens.cpu().pin_memory(), ids.cpu().pin_memory(), gates.cpu().pin_memory()
-  h_out = torch.empty(EP_TOKENS, EP_N, dtype=torch.bfloat16).pin_memory()
-  d_tok, d_ids, d_gates = torch.empty_like(tokens), torch.empty_like(ids), torch.empty_like(gates)
-
-  def e2e_step():
-    d_tok.copy_(h_tok, non_blocking=True)
-    d_ids.copy_(h_ids, non_blocking=True)
-    d_gates.copy_(h_gates, non_blocking=True)
-    yy, _ = layer(d_tok, d_ids, d_gates)
-    h_out.copy_(yy, non_blocking=True)
-
-  for _ in range(2):
-    e2e_step()
+  # Every step copies its inputs from pinned host memory and its result back; the layer's
+  # HostPipeline runs those copies beside the neighbouring steps' computation (two staging slots,
+  # two result buffers).  The region ends when the last step's result is in host memory.
+  from tokamax_b200.expert_parallel import HostPipeline
+  h_outs = [torch.empty(EP_TOKENS, EP_N, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+  pipe = HostPipeline(layer, depth=2)
+  last = None
+  for i in range(3):
+    last = pipe.submit(h_tok, h_ids, h_gates, h_outs[i % 2])
+  pipe.drain()
   barrier()
   s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   s2.record(stream)
-  for _ in range(args.steps):
-    e2e_step()
+  for i in range(args.steps):
+    last = pipe.submit(h_tok, h_ids, h_gates, h_outs[i % 2])
+  stream.wait_event(last)          # the last result has reached the host
   e2.record(stream)
+  pipe.drain()
   barrier()
   e2e_total = s2.elapsed_time(e2)
+  e2e_ok = bool(torch.equal(h_outs[(args.steps - 1) % 2], y.cpu())) if args.steps > 0 else True
 
   gemm_mean = float(np.mean(gemm_ms)) if gemm_ms else 0.0
   stats = torch.tensor([total_ms, e2e_total, gemm_mean, max_err, worst_ratio, 0.0 if gs_exact else 1.0],
@@ -631,7 +633,11 @@ def run_expert_parallel(args, peaks, world, rank, local_rank):
                  "group_sizes_exact": float(stats[5]) == 0.0, "ok": parity_ok},
       "e2e": {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
               "h2d_bytes_per_step": world * (h_tok.numel() * 2 + h_ids.numel() * 4 + h_gates.numel() * 4),
-              "d2h_bytes_per_step": world * h_out.numel() * 2, "ms_per_step": e2e_ms},
+              "d2h_bytes_per_step": world * h_outs[0].numel() * 2, "ms_per_step": e2e_ms,
+              "api": "tokamax_b200.expert_parallel.HostPipeline.submit (pinned host tensors in and out)",
+              "pipeline": "depth 2: a step's copies run beside the neighbouring steps' computation; "
+                          "timed until the last step's result is in host memory",
+              "result_equals_device_run": e2e_ok},
       "gpu_launches": args.steps * launches_per_step,
       "gpu_launches_per_step": launches_per_step,
       "clocks": clocks.summary(),

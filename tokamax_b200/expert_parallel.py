@@ -523,3 +523,72 @@ class ExpertParallelMoE:
     plan = DispatchPlan(st["pos"], [], [0] * w, st["plan"][:0], t, top_k,
                         local_group_sizes=st["plan"][:self.local_experts])
     return y, plan
+
+
+class HostPipeline:
+  """The layer on PINNED HOST buffers, step after step: tokens, routing and gates are copied to
+  the device, the layer runs, the result is copied back -- with the copies of one step running
+  beside the computation of its neighbours (a copy-in stream, the caller's stream, a copy-out
+  stream; `depth` device staging slots).  A serving loop calls `submit` once per step and reads
+  a step's output after waiting for the event `submit` returned (or after `drain`).
+
+  Nothing is skipped: every step's inputs cross PCIe in that step and its output is written to
+  host memory; what the pipeline removes is the idle time of the copy engines while the GPU
+  computes and of the GPU while they copy."""
+
+  def __init__(self, layer: ExpertParallelMoE, depth: int = 2):
+    if depth < 1:
+      raise ValueError("depth must be at least 1")
+    self.layer = layer
+    self.depth = depth
+    self._slots = None
+    self._next = 0
+    self._copy_in = None
+    self._copy_out = None
+
+  def _make_slots(self, h_tok, h_ids, h_gates):
+    dev = self.layer.rhs_local.device
+    self._copy_in = torch.cuda.Stream(device=dev)
+    self._copy_out = torch.cuda.Stream(device=dev)
+    self._slots = []
+    for _ in range(self.depth):
+      self._slots.append(dict(
+          tok=torch.empty(h_tok.shape, dtype=h_tok.dtype, device=dev),
+          ids=torch.empty(h_ids.shape, dtype=h_ids.dtype, device=dev),
+          gates=torch.empty(h_gates.shape, dtype=h_gates.dtype, device=dev),
+          in_ready=torch.cuda.Event(), computed=torch.cuda.Event(), out_done=torch.cuda.Event(), used=False))
+
+  def submit(self, h_tok: torch.Tensor, h_ids: torch.Tensor, h_gates: torch.Tensor, h_out: torch.Tensor):
+    """Enqueues one step; returns the CUDA event after which `h_out` holds its result."""
+    for h in (h_tok, h_ids, h_gates, h_out):
+      if h.is_cuda or not h.is_pinned():
+        raise ValueError("HostPipeline takes pinned host tensors")
+    if self._slots is None or self._slots[0]["tok"].shape != h_tok.shape or self._slots[0]["ids"].shape != h_ids.shape:
+      self.drain()
+      self._make_slots(h_tok, h_ids, h_gates)
+    slot = self._slots[self._next % self.depth]
+    self._next += 1
+    main = torch.cuda.current_stream(self.layer.rhs_local.device)
+    if slot["used"]:
+      self._copy_in.wait_event(slot["computed"])     # the step that last read this slot is done with it
+    with torch.cuda.stream(self._copy_in):
+      slot["tok"].copy_(h_tok, non_blocking=True)
+      slot["ids"].copy_(h_ids, non_blocking=True)
+      slot["gates"].copy_(h_gates, non_blocking=True)
+      slot["in_ready"].record(self._copy_in)
+    main.wait_event(slot["in_ready"])
+    y, _ = self.layer(slot["tok"], slot["ids"], slot["gates"])
+    slot["computed"].record(main)
+    slot["used"] = True
+    self._copy_out.wait_event(slot["computed"])
+    with torch.cuda.stream(self._copy_out):
+      h_out.copy_(y, non_blocking=True)
+      slot["out_done"].record(self._copy_out)
+    y.record_stream(self._copy_out)
+    return slot["out_done"]
+
+  def drain(self) -> None:
+    """Waits until every submitted step's output is in host memory."""
+    for s in (self._copy_in, self._copy_out):
+      if s is not None:
+        s.synchronize()
