@@ -244,6 +244,34 @@ def test_fused_layer_world1_public_call():
   assert torch.equal(y, y3)
 
 
+def test_host_pipeline_matches_device_calls_step_by_step():
+  """HostPipeline: five steps with different pinned host inputs, two staging slots; every step's
+  host result equals the layer called on device tensors with the same inputs."""
+  _capi()
+  from tokamax_b200.expert_parallel import ExpertParallelMoE, HostPipeline
+  t, k, n, g, top_k = 512, 256, 384, 16, 4
+  rng = np.random.default_rng(61)
+  rhs = torch.from_numpy(rng.normal(0, k ** -0.5, (g, k, n)).astype(np.float32)).bfloat16()
+  layer = ExpertParallelMoE(rhs.cuda(), g)
+  steps = []
+  for i in range(5):
+    tok = torch.from_numpy(rng.normal(0, 1, (t, k)).astype(np.float32)).bfloat16().pin_memory()
+    ids, gates = arg_specs.topk_routing(t, g, top_k, seed=70 + i)
+    steps.append((tok, torch.from_numpy(ids).pin_memory(), torch.from_numpy(gates).pin_memory(),
+                  torch.empty(t, n, dtype=torch.bfloat16).pin_memory()))
+  pipe = HostPipeline(layer, depth=2)
+  events = [pipe.submit(*s) for s in steps]
+  events[1].synchronize()
+  want1, _ = layer(steps[1][0].cuda(), steps[1][1].cuda(), steps[1][2].cuda())
+  assert torch.equal(steps[1][3], want1.cpu())       # readable as soon as its own event has fired
+  pipe.drain()
+  for tok, ids, gates, out in steps:
+    want, _ = layer(tok.cuda(), ids.cuda(), gates.cuda())
+    assert torch.equal(out, want.cpu())
+  with pytest.raises(ValueError):
+    pipe.submit(steps[0][0].clone(), steps[0][1], steps[0][2], steps[0][3])   # not pinned
+
+
 def test_barrier_wait_runs_out_and_reports_status():
   """A flag that nothing sets: the barrier kernel gives up after its budget, the status word says
   so, and the device keeps working."""
