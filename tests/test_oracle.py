@@ -241,3 +241,29 @@ def test_reference_words_of_the_once_per_rank_dispatch_known_answer():
   ids2 = [np.array([[2, 9, 3]], np.int32), np.array([[-1, 0, 1]], np.int32)]
   refs2 = moe_ref.ep_reference_words_ref(ids2, 4)
   assert refs2[1].tolist() == [0, (1 << 24) | 0] and refs2[0].tolist() == [0, (1 << 24) | 0]
+
+
+def test_single_term_w8a8_exceeds_the_tolerance_and_the_two_term_split_does_not():
+  """Why the 8-bit kernels multiply TWO activation planes (hi + lo) per weight: rounding the
+  activations to one e4m3 value per element (per-row absmax scale, a single MMA) leaves errors
+  above the 5e-2 + 5e-2 |x| bound of 8-bit weights on DeepSeek-shaped rows (K = 7168), the
+  two-term split stays far inside it.  Float64 reference on the CPU."""
+  torch.manual_seed(0)
+  k, n, m = 7168, 128, 256
+  x = torch.randn(m, k).bfloat16()
+  w = torch.randn(k, n) * k ** -0.5
+  s = w.abs().amax(0) / 448.0
+  wq = (w / s).to(torch.float8_e4m3fn).float()
+  exact = (x.double() @ wq.double()) * s.double()
+
+  def rows_e4m3(v):
+    rs = v.abs().amax(1, keepdim=True) / 448.0
+    return (v / rs).to(torch.float8_e4m3fn).float() * rs
+
+  hi = rows_e4m3(x.float())
+  lo = rows_e4m3(x.float() - hi)
+  tol = 5e-2 + 5e-2 * exact.abs()
+  one = ((hi.double() @ wq.double()) * s.double() - exact).abs() / tol
+  two = (((hi + lo).double() @ wq.double()) * s.double() - exact).abs() / tol
+  assert one.max() > 1.0          # measured 2.2 x the tolerance, ~1 % of the elements over it
+  assert two.max() < 0.2          # measured 0.05
