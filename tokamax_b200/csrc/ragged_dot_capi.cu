@@ -448,8 +448,9 @@ int run_rows(const void* a, const void* b, bool b_cols_contiguous, const int32_t
   p.prefetch_blocks = env_int("TKMX_PREFETCH", 0, 0, 64);
   p.prefetch_cold_only = env_int("TKMX_PREFETCH_COLD_ONLY", 1, 0, 1);
   // Equal swapped tiles instead of full + short ones: off by default.  Measured on B200 it
-  // lost (cfg4: 0.40 against 0.24 ms): a swapped tile's transposed epilogue stores 2 bytes per
-  // lane and grows with the tile's rows, which outweighs the MMA time saved.
+  // lost (cfg4 forward 0.215 against 0.209 ms, dlhs 0.243 against 0.218): a swapped tile's
+  // transposed epilogue stores 2 bytes per lane and grows with the tile's rows, which outweighs
+  // the MMA time saved.
   p.balance_tiles = env_int("TKMX_BALANCE_TILES", 0, 0, 1);
 
   // 16-bit outputs: blocks of 32 rows x 64 columns that are not ragged leave by TMA store.
