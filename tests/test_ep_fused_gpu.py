@@ -123,6 +123,8 @@ def _run_virtual(capi, w, t, k, n, g, top_k, pair, seed, bad_ids=False, dtype=to
       ids = ids.copy()
       ids[rng.random(ids.shape) < 0.05] = g + 3      # dropped pairs
       ids[rng.random(ids.shape) < 0.03] = -1
+      twice = rng.random(t) < 0.1                    # a token that names one expert twice
+      ids[twice, 1] = ids[twice, 0]
     idss.append(torch.from_numpy(ids))
     gatess.append(torch.from_numpy(gates))
   vr = VirtualRanks(capi, w, g, t, top_k, k, n, dtype, once=once)

@@ -504,7 +504,8 @@ __device__ __forceinline__ void ep_copy_rows(const EpFusedParams& ep, const int*
       if (ref != 0u) {
         const int le1 = static_cast<int>(ref >> kEpRefRowBits) - 1;
         const int r1 = static_cast<int>(ref & ((1u << kEpRefRowBits) - 1u));
-        if (le1 < 0 || le1 >= le || r1 < row_start[le1] || r1 >= row_start[le1 + 1]) {
+        // the original lies in an earlier expert, or in this one when a token names an expert twice
+        if (le1 < 0 || le1 > le || r1 == row || r1 < row_start[le1] || r1 >= row_start[le1 + 1]) {
           atomicCAS(status, 0, kDevEpOverflow);
         } else if (ep_wait_sum(present + le1, announced + le1, static_cast<uint32_t>(row_start[le1 + 1] - row_start[le1]),
                                abort_flag, status, budget_ns)) {
