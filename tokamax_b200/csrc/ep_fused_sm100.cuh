@@ -462,7 +462,7 @@ __device__ __forceinline__ bool ep_wait_sum(const uint32_t* a, const uint32_t* b
 // Receiving side of the once-per-rank form, one warp: rows of this rank's receive buffer,
 // kEpItemRows at a time in expert order.  Once every row of an expert is either present or
 // announced (its reference word is written), the duplicates among them are copied from their
-// originals, which lie in an earlier expert of the same buffer, and counted as copied.
+// originals, which lie in an earlier expert of the same buffer (or the same expert, for a token that names it twice), and counted as copied.
 // `row_start` [G/W + 1]: first receive-buffer row of every local expert (shared memory).
 __device__ __forceinline__ void ep_copy_rows(const EpFusedParams& ep, const int* row_start, int lane,
                                              volatile int* abort_flag, int32_t* status, uint64_t budget_ns) {
