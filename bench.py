@@ -644,6 +644,24 @@ def run_expert_parallel(args, peaks, world, rank, local_rank):
                 "algorithmic_bytes_per_launch": g_bytes, "frac_tensor": rl["frac_tensor"],
                 "frac_hbm": rl["frac_hbm"],
                 "peak_source": peaks["source"] + (", HBM copy" if hbm else ", bf16 sustained (kernel timed inside a long step)")}
+    if world > 1 and layer.exchange == "fused":
+      # What one launch of the fused kernel pushes over NVLink from rank 0 (every rank's routing
+      # has the same statistics): token rows to remote owners -- one per (token, remote rank) when
+      # a token crosses to a rank once, else one per remote pair -- plus the output rows it returns
+      # to remote sources (1/world of the rows it multiplies stay local).  Link time at the
+      # measured peer-copy rate of this pool, 770 GB/s per direction.
+      owner = ep_routing(0)[0] // gl
+      remote = owner != 0
+      if layer.exchange_name.endswith("once)"):
+        sent_rows = sum(int(((owner == d).any(1)).sum()) for d in range(1, world))
+      else:
+        sent_rows = int(remote.sum())
+      link_bytes = sent_rows * EP_K * 2 + rows_rank * (world - 1) / world * EP_N * 2
+      t_link = link_bytes / 770e9
+      t_target = max(g_flops / (peak_tf * 1e12), t_link)
+      roofline.update({"nvlink_bytes_per_launch": float(link_bytes), "t_link_ms": t_link * 1e3,
+                       "nvlink_peak": "770 GB/s per direction (measured peer copy on this pool)",
+                       "frac_of_max_tensor_link": t_target / (g_ms * 1e-3)})
   else:
     roofline = None
   cfg = ep_config(world, layer.exchange, layer.num_chunks)
