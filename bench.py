@@ -722,7 +722,7 @@ def main():
                   help="row exchange of the expert-parallel layer (default: the fused kernel; fused_once / "
                        "fused_pairs force a token to cross to a rank once / once per routed pair)")
   ap.add_argument("--ep-chunks", type=int, default=0,
-                  help="expert chunks of the p2p / nccl exchanges whose transfers overlap the neighbouring GEMMs")
+                  help="expert chunks of the nccl exchange whose transfers overlap the neighbouring GEMMs")
   ap.add_argument("--kernel-only", action="store_true",
                   help="exactly --steps launches of the timed region, no padding for the clock sampler")
   ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel suite of the N = 1 line")
